@@ -1,0 +1,92 @@
+"""The CPU oracle against the golden vectors produced by the reference's own code
+(tests/golden/make_golden.py).  Everything here runs without a GPU."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attn_jvp_oracle as orc
+from tests.conftest import GOLDEN
+from tests.golden.make_golden import CASES
+
+
+def _load(name):
+    B, L, H, D, ts, qkn, seed = CASES[name]
+    g = np.load(GOLDEN / f"{name}.npz")
+    ins = orc.make_inputs(B, L, H, D, seed=seed, tangent_scale=ts, qk_norm=qkn, n_extra=1)
+    # the generator must reproduce the inputs the golden outputs were made from
+    chk = np.array([float(x.double().sum()) for x in ins])
+    np.testing.assert_allclose(chk, g["checksum"], rtol=0, atol=1e-3)
+    return g, ins
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_base_jvp_matches_reference(name):
+    g, (q, k, v, tq, tk, tv, dout) = _load(name)
+    o, do = orc.attn_jvp_base(q, k, v, tq, tk, tv)
+    # same code path, same machine arithmetic: fp32 round-off only
+    np.testing.assert_allclose(o.numpy(), g["base_o"], rtol=0, atol=2e-6)
+    np.testing.assert_allclose(do.numpy(), g["base_do"], rtol=0, atol=2e-6)
+    assert g["raw_vs_base_maxabs"].max() < 5e-6
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_closed_form_matches_reference(name):
+    g, (q, k, v, tq, tk, tv, dout) = _load(name)
+    o, do, lse = orc.attn_jvp_closed_form(q, k, v, tq, tk, tv)
+    assert orc.rel_l2(o, torch.from_numpy(g["base_o"])) < 2e-6
+    assert orc.rel_l2(do, torch.from_numpy(g["base_do"])) < 2e-6
+    # the reference Triton kernels (CPU interpreter, fp32) as a third witness, incl. LSE
+    assert orc.rel_l2(o, torch.from_numpy(g["tri_o"])) < 2e-6
+    assert orc.rel_l2(do, torch.from_numpy(g["tri_do"])) < 2e-6
+    np.testing.assert_allclose(lse.float().numpy(), g["tri_lse"], rtol=0, atol=5e-6)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_online_recurrence_matches_reference_kernel(name):
+    g, (q, k, v, tq, tk, tv, dout) = _load(name)
+    o, do, lse = orc.attn_jvp_online(q, k, v, tq, tk, tv, block_kv=128)
+    assert orc.rel_l2(o, torch.from_numpy(g["tri_o"])) < 2e-6
+    assert orc.rel_l2(do, torch.from_numpy(g["tri_do"])) < 2e-6
+    np.testing.assert_allclose(lse.float().numpy(), g["tri_lse"], rtol=0, atol=5e-6)
+    # block size must not matter
+    o2, do2, lse2 = orc.attn_jvp_online(q, k, v, tq, tk, tv, block_kv=64)
+    assert orc.rel_l2(o2, o) < 1e-12 and orc.rel_l2(do2, do) < 1e-12
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_backward_matches_reference(name):
+    g, (q, k, v, tq, tk, tv, dout) = _load(name)
+    dq, dk, dv = orc.attn_bwd_base(q, k, v, dout)
+    for got, key in ((dq, "raw_dq"), (dk, "raw_dk"), (dv, "raw_dv")):
+        assert orc.rel_l2(got, torch.from_numpy(g[key])) < 2e-6
+    dq2, dk2, dv2 = orc.attn_bwd_closed_form(q, k, v, dout)
+    for got, key in ((dq2, "raw_dq"), (dk2, "raw_dk"), (dv2, "raw_dv")):
+        assert orc.rel_l2(got, torch.from_numpy(g[key])) < 2e-6
+
+
+def test_rms_norm_matches_reference():
+    name = "d72_l256_qknorm"
+    g, (q, k, v, tq, tk, tv, dout) = _load(name)
+    np.testing.assert_allclose(q.numpy(), g["normed_q"], rtol=0, atol=1e-6)
+    np.testing.assert_allclose(tq.numpy(), g["normed_tq"], rtol=0, atol=1e-6)
+    np.testing.assert_allclose(k.numpy(), g["normed_k"], rtol=0, atol=1e-6)
+    np.testing.assert_allclose(tk.numpy(), g["normed_tk"], rtol=0, atol=1e-6)
+
+
+def test_bf16_emulation_floor():
+    """The rounding points of the bf16 kernel leave a wide margin under the 2e-2 bar."""
+    q, k, v, tq, tk, tv = orc.make_inputs(1, 256, 2, 72, seed=5, tangent_scale=0.1)
+    qb, kb, vb, tqb, tkb, tvb = (x.bfloat16().float() for x in (q, k, v, tq, tk, tv))
+    o_ref, do_ref, _ = orc.attn_jvp_closed_form(q, k, v, tq, tk, tv)
+    o, do, _ = orc.attn_jvp_online(qb, kb, vb, tqb, tkb, tvb, emulate_bf16=True, dtype=torch.float32)
+    assert orc.rel_l2(o.bfloat16(), o_ref) < 1e-2
+    assert orc.rel_l2(do.bfloat16(), do_ref) < 1e-2
+
+
+def test_config_shapes_and_flops():
+    assert orc.CONFIGS["C2"][:4] == (256, 256, 16, 72)
+    assert orc.CONFIGS["C3"][:4] == (64, 1024, 16, 72)
+    assert abs(orc.flops_dual_fwd(256, 16, 256, 256, 72) - 231.9e9) < 0.1e9
+    assert abs(orc.flops_dual_fwd(64, 16, 1024, 1024, 72) - 927.7e9) < 0.1e9
+    assert abs(orc.flops_dual_fwd(8, 12, 256, 256, 64) - 4.83e9) < 0.01e9
