@@ -1,0 +1,110 @@
+"""ctypes binding of the C ABI in include/dmf_attn.h.
+
+The library is the only compute path of this package: if it cannot be loaded the
+import fails; nothing falls back to PyTorch or to the CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from pathlib import Path
+
+from . import build as _build
+
+ABI_VERSION = 1
+BF16, FP16 = 0, 1
+
+STATUS_NAMES = {
+    0: "OK", 1: "ERR_NULL", 2: "ERR_DTYPE", 3: "ERR_HEAD_DIM", 4: "ERR_SEQLEN", 5: "ERR_SHAPE",
+    6: "ERR_STRIDE", 7: "ERR_ALIGN", 8: "ERR_DEVICE", 9: "ERR_TENSOR_MAP", 10: "ERR_LAUNCH",
+    11: "ERR_WORKSPACE", 12: "ERR_TIMEOUT",
+}
+
+# every symbol include/dmf_attn.h declares
+EXPORTS = (
+    "dmf_attn_abi_version", "dmf_attn_status_string", "dmf_attn_fwd_dual", "dmf_attn_fwd",
+    "dmf_attn_bwd", "dmf_attn_bwd_workspace_bytes", "dmf_attn_check_status_word",
+    "dmf_attn_validate_fwd", "dmf_attn_validate_bwd",
+)
+
+
+class Tensor4(C.Structure):
+    """dmf_attn_tensor: base pointer + element strides of a (B, L, H, D) tensor."""
+    _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_l", C.c_int64), ("stride_h", C.c_int64)]
+
+
+class FwdArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("seqlen_q", C.c_int32), ("seqlen_kv", C.c_int32), ("heads", C.c_int32),
+        ("head_dim", C.c_int32), ("dtype", C.c_int32), ("softmax_scale", C.c_float), ("reserved", C.c_int32),
+        ("q", Tensor4), ("k", Tensor4), ("v", Tensor4),
+        ("tq", Tensor4), ("tk", Tensor4), ("tv", Tensor4),
+        ("o", Tensor4), ("to", Tensor4),
+        ("lse", C.c_void_p), ("status_word", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
+class BwdArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("seqlen_q", C.c_int32), ("seqlen_kv", C.c_int32), ("heads", C.c_int32),
+        ("head_dim", C.c_int32), ("dtype", C.c_int32), ("softmax_scale", C.c_float), ("reserved", C.c_int32),
+        ("dout", Tensor4), ("q", Tensor4), ("k", Tensor4), ("v", Tensor4), ("o", Tensor4),
+        ("lse", C.c_void_p),
+        ("dq", Tensor4), ("dk", Tensor4), ("dv", Tensor4),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("status_word", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
+class DmfAttnError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"dmf_attn: {STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+
+
+_lock = threading.Lock()
+_lib = None
+
+
+def library_path() -> Path:
+    return _build.LIB
+
+
+def load() -> C.CDLL:
+    """Load (building first if the in-tree .so is missing or stale) and type the library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = _build.build()
+        lib = C.CDLL(str(path))
+        lib.dmf_attn_abi_version.restype = C.c_int
+        lib.dmf_attn_status_string.restype = C.c_char_p
+        lib.dmf_attn_status_string.argtypes = [C.c_int]
+        for name in ("dmf_attn_fwd_dual", "dmf_attn_fwd"):
+            fn = getattr(lib, name)
+            fn.restype = C.c_int
+            fn.argtypes = [C.POINTER(FwdArgs)]
+        lib.dmf_attn_bwd.restype = C.c_int
+        lib.dmf_attn_bwd.argtypes = [C.POINTER(BwdArgs)]
+        lib.dmf_attn_bwd_workspace_bytes.restype = C.c_size_t
+        lib.dmf_attn_bwd_workspace_bytes.argtypes = [C.c_int32] * 5
+        lib.dmf_attn_check_status_word.restype = C.c_int
+        lib.dmf_attn_check_status_word.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+        lib.dmf_attn_validate_fwd.restype = C.c_int
+        lib.dmf_attn_validate_fwd.argtypes = [C.POINTER(FwdArgs), C.c_int]
+        lib.dmf_attn_validate_bwd.restype = C.c_int
+        lib.dmf_attn_validate_bwd.argtypes = [C.POINTER(BwdArgs)]
+        got = lib.dmf_attn_abi_version()
+        if got != ABI_VERSION:
+            raise ImportError(f"libdmf_attn.so has ABI version {got}, this package expects {ABI_VERSION}")
+        _lib = lib
+        return lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise DmfAttnError(status, load().dmf_attn_status_string(status).decode())

@@ -1,0 +1,521 @@
+// Forward attention kernels for sm_100a: the fused forward + tangent ("dual")
+// pass and the plain forward, one persistent warp-specialised kernel template.
+//
+// Work decomposition.  A tile is 128 consecutive query rows of one (batch, head).
+// CTA i handles tiles i, i + gridDim.x, ... (one CTA per SM).  Inside a tile the
+// KV sequence is walked in blocks of 128 rows with a single online softmax:
+//
+//   S  = Q K^T                    (tcgen05.mma, operands in shared memory)
+//   dS = dQ K^T + Q dK^T          (two MMAs into one accumulator)
+//   P  = exp2(S*c - m),  G = P * dS * scale        (softmax warps, registers)
+//   O += P V,   T += P dV + G V   (tcgen05.mma, P / G read from tensor memory)
+//
+// running m (lazily updated max), l = sum P, mu = sum G; epilogue
+//   o = O / l,   to = T / l - (mu / l) o,   lse = ln2 * (m + log2 l).
+//
+// Warp roles (192 threads):
+//   warp 0     TMA producer: Q/dQ tile, then K/dK and V/dV blocks through two
+//              shared-memory rings; also owns the tensor-memory allocation
+//   warp 1     MMA issuer (one thread)
+//   warps 2-5  softmax + correction + epilogue; thread = query row,
+//              tensor-memory lane quarter = warp_id % 4
+//
+// Tensor memory columns (fp32 accumulators, 128 lanes):
+//   [0,128)   S; P (16-bit, 64 columns) is written over it
+//   [128,256) dS; G is written over it      (plain forward: second S buffer)
+//   [256, 256+DPAD)         O
+//   [256+DPAD, 256+2*DPAD)  T               (dual only)
+//
+// Head dim D is handled as a 64-column main part (128-byte swizzle) plus a tail
+// of TAIL in {0,16,32,64} columns (swizzle of 2*TAIL bytes); columns past D in
+// the tail are zero-filled by TMA and contribute nothing.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include "sm100_ptx.cuh"
+
+namespace dmf {
+
+constexpr int kBlockQ = 128;
+constexpr int kBlockKV = 128;
+constexpr int kFwdThreads = 192;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8
+
+// Codes written to the status word when a wait gives up: role * 100 + barrier.
+constexpr int kRoleProducer = 100, kRoleMma = 200, kRoleSoftmax = 300;
+
+struct FwdParams {
+  // TMA maps of (D, L, H, B) views; "main" = columns [0,64), "tail" = [64, 64+TAIL)
+  CUtensorMap q_main, q_tail, k_main, k_tail, v_main, v_tail;
+  CUtensorMap tq_main, tq_tail, tk_main, tk_tail, tv_main, tv_tail;
+  void* o;
+  void* to;
+  float* lse;
+  int64_t o_sb, o_sl, o_sh;
+  int64_t to_sb, to_sl, to_sh;
+  int32_t* status_word;
+  int batch, heads, seqlen_q, seqlen_kv, head_dim;
+  int num_q_tiles, num_tiles;
+  float scale, scale_log2e;
+};
+
+template <int TAIL, bool kDual>
+struct FwdTraits {
+  static constexpr int kDPad = 64 + TAIL;
+  static constexpr int kMainBytes = 128 * 128;
+  static constexpr int kTailBytes = 128 * TAIL * 2;
+  static constexpr int kTileBytes = kMainBytes + kTailBytes;
+  static constexpr int kGroup = kDual ? 2 : 1;  // primal (+ tangent) tile per ring slot
+  static constexpr int kGroupBytes = kGroup * kTileBytes;
+  static constexpr int kStagesK = 2;
+  static constexpr int kStagesV = (kDual && TAIL == 32) ? 1 : 2;
+  static constexpr int kStagesK_ = (kDual && TAIL == 64) ? 1 : kStagesK;
+  static constexpr int kStagesV_ = (kDual && TAIL == 64) ? 1 : kStagesV;
+  static constexpr int kTileSmem = kGroupBytes * (1 + kStagesK_ + kStagesV_);
+  // barriers
+  static constexpr int kBarQFull = 0, kBarQEmpty = 1, kBarSFull = 2, kBarDSFull = 3, kBarPFull = 4,
+                       kBarGFull = 5, kBarAccFull = 6, kBarKFull = 7,
+                       kBarKEmpty = kBarKFull + kStagesK_, kBarVFull = kBarKEmpty + kStagesK_,
+                       kBarVEmpty = kBarVFull + kStagesV_, kNumBars = kBarVEmpty + kStagesV_;
+  static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kTileSmem + kNumBars * 8 + 16;
+  // tensor memory columns
+  static constexpr uint32_t kColS = 0, kColDS = 128, kColO = 256, kColT = 256 + kDPad;
+  static constexpr uint32_t kTmemCols = 512;
+  // swizzle of the tail part
+  static constexpr uint32_t kTailSwizzle = TAIL == 64 ? kSwizzle128 : (TAIL == 32 ? kSwizzle64 : kSwizzle32);
+  static constexpr uint32_t kTailRowBytes = 2 * TAIL;
+};
+
+// ---- MMA issue helpers (one thread) ------------------------------------------
+
+// acc[128 x 128] (+)= A[128 x D] * B[128 x D]^T, both operands K-major in shared memory.
+template <int TAIL, typename TR>
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile,
+                                         uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+    const uint64_t ad = make_smem_desc(a_tile + kk * 32, 16, 1024, kSwizzle128);
+    const uint64_t bd = make_smem_desc(b_tile + kk * 32, 16, 1024, kSwizzle128);
+    mma_ss(d_tmem, ad, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+#pragma unroll
+  for (int kk = 0; kk < TAIL / 16; ++kk) {
+    const uint64_t ad = make_smem_desc(a_tile + TR::kMainBytes + kk * 32, 16, 8 * TR::kTailRowBytes,
+                                       TR::kTailSwizzle);
+    const uint64_t bd = make_smem_desc(b_tile + TR::kMainBytes + kk * 32, 16, 8 * TR::kTailRowBytes,
+                                       TR::kTailSwizzle);
+    mma_ss(d_tmem, ad, bd, idesc, 1u);
+  }
+}
+
+// acc[128 x DPAD] (+)= A[128 x 128] * V[128 x DPAD]; A is 16-bit in tensor memory
+// (two elements per column), V is MN-major (row = kv index, D contiguous) in shared memory.
+template <int TAIL, typename TR>
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t a_tmem, uint32_t v_tile,
+                                         uint32_t idesc_main, uint32_t idesc_tail, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < kBlockKV / 16; ++kk) {
+    const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
+    const uint64_t bd = make_smem_desc(v_tile + kk * (16 * 128), 8192, 1024, kSwizzle128);
+    mma_ts(d_tmem, a_tmem + kk * 8, bd, idesc_main, acc);
+    if constexpr (TAIL > 0) {
+      const uint64_t bt = make_smem_desc(v_tile + TR::kMainBytes + kk * (16 * TR::kTailRowBytes),
+                                         TR::kTailBytes, 8 * TR::kTailRowBytes, TR::kTailSwizzle);
+      mma_ts(d_tmem + 64, a_tmem + kk * 8, bt, idesc_tail, acc);
+    }
+  }
+}
+
+// ---- the kernel ---------------------------------------------------------------
+
+template <typename T, int TAIL, bool kDual>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_kernel(const __grid_constant__ FwdParams p) {
+  using TR = FwdTraits<TAIL, kDual>;
+  constexpr int DPAD = TR::kDPad;
+  constexpr bool kBf16 = Pack2<T>::kIsBf16;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t s_q = smem_u32(smem);
+  const uint32_t s_k = s_q + TR::kGroupBytes;
+  const uint32_t s_v = s_k + TR::kStagesK_ * TR::kGroupBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TR::kTileSmem);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + TR::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) -> uint32_t { return bar0 + 8u * static_cast<uint32_t>(i); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kv_blocks = p.seqlen_kv / kBlockKV;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < TR::kNumBars; ++i) {
+      const bool softmax_arrives = (i == TR::kBarPFull || i == TR::kBarGFull);
+      mbar_init(bar(i), softmax_arrives ? 128u : 1u);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), TR::kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // =========================== TMA producer ===============================
+    if (lane == 0) {
+      prefetch_tensor_map(&p.q_main);
+      prefetch_tensor_map(&p.k_main);
+      prefetch_tensor_map(&p.v_main);
+      uint32_t kcnt = 0, vcnt = 0, tcnt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcnt) {
+        const int bh = tile / p.num_q_tiles;
+        const int q0 = (tile % p.num_q_tiles) * kBlockQ;
+        const int b = bh / p.heads, h = bh % p.heads;
+        ok = mbar_wait(bar(TR::kBarQEmpty), (tcnt & 1u) ^ 1u, abort_flag, p.status_word,
+                       kRoleProducer + TR::kBarQEmpty);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar(TR::kBarQFull), TR::kGroupBytes);
+        tma_load_4d(s_q, &p.q_main, bar(TR::kBarQFull), 0, q0, h, b);
+        if constexpr (TAIL > 0) tma_load_4d(s_q + TR::kMainBytes, &p.q_tail, bar(TR::kBarQFull), 64, q0, h, b);
+        if constexpr (kDual) {
+          tma_load_4d(s_q + TR::kTileBytes, &p.tq_main, bar(TR::kBarQFull), 0, q0, h, b);
+          if constexpr (TAIL > 0)
+            tma_load_4d(s_q + TR::kTileBytes + TR::kMainBytes, &p.tq_tail, bar(TR::kBarQFull), 64, q0, h, b);
+        }
+        for (int j = 0; j < num_kv_blocks; ++j) {
+          const int kv0 = j * kBlockKV;
+          {
+            const uint32_t s = kcnt % TR::kStagesK_, ph = (kcnt / TR::kStagesK_) & 1u;
+            ok = mbar_wait(bar(TR::kBarKEmpty + s), ph ^ 1u, abort_flag, p.status_word,
+                           kRoleProducer + TR::kBarKEmpty);
+            if (!ok) break;
+            const uint32_t dst = s_k + s * TR::kGroupBytes, fb = bar(TR::kBarKFull + s);
+            mbar_arrive_expect_tx(fb, TR::kGroupBytes);
+            tma_load_4d(dst, &p.k_main, fb, 0, kv0, h, b);
+            if constexpr (TAIL > 0) tma_load_4d(dst + TR::kMainBytes, &p.k_tail, fb, 64, kv0, h, b);
+            if constexpr (kDual) {
+              tma_load_4d(dst + TR::kTileBytes, &p.tk_main, fb, 0, kv0, h, b);
+              if constexpr (TAIL > 0)
+                tma_load_4d(dst + TR::kTileBytes + TR::kMainBytes, &p.tk_tail, fb, 64, kv0, h, b);
+            }
+            ++kcnt;
+          }
+          {
+            const uint32_t s = vcnt % TR::kStagesV_, ph = (vcnt / TR::kStagesV_) & 1u;
+            ok = mbar_wait(bar(TR::kBarVEmpty + s), ph ^ 1u, abort_flag, p.status_word,
+                           kRoleProducer + TR::kBarVEmpty);
+            if (!ok) break;
+            const uint32_t dst = s_v + s * TR::kGroupBytes, fb = bar(TR::kBarVFull + s);
+            mbar_arrive_expect_tx(fb, TR::kGroupBytes);
+            tma_load_4d(dst, &p.v_main, fb, 0, kv0, h, b);
+            if constexpr (TAIL > 0) tma_load_4d(dst + TR::kMainBytes, &p.v_tail, fb, 64, kv0, h, b);
+            if constexpr (kDual) {
+              tma_load_4d(dst + TR::kTileBytes, &p.tv_main, fb, 0, kv0, h, b);
+              if constexpr (TAIL > 0)
+                tma_load_4d(dst + TR::kTileBytes + TR::kMainBytes, &p.tv_tail, fb, 64, kv0, h, b);
+            }
+            ++vcnt;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ============================ MMA issuer ================================
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(kBf16, false, false, 128, 128);
+      constexpr uint32_t idesc_pv_main = make_idesc(kBf16, false, true, 128, 64);
+      constexpr uint32_t idesc_pv_tail = make_idesc(kBf16, false, true, 128, TAIL > 0 ? TAIL : 16);
+      const uint32_t t_s = tmem + TR::kColS, t_ds = tmem + TR::kColDS;
+      const uint32_t t_o = tmem + TR::kColO, t_t = tmem + TR::kColT;
+      uint32_t kcnt = 0, vcnt = 0, tcnt = 0, pcnt = 0, gcnt = 0, scnt = 0;
+      bool ok = true;
+      auto wait = [&](int b_, uint32_t parity) -> bool {
+        return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_);
+      };
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcnt) {
+        ok = wait(TR::kBarQFull, tcnt & 1u);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if constexpr (kDual) {
+          // block 0: S and dS
+          uint32_t sk = kcnt % TR::kStagesK_;
+          ok = wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK_) & 1u);
+          if (!ok) break;
+          tc_fence_after_sync();
+          uint32_t kt = s_k + sk * TR::kGroupBytes;
+          issue_qk<TAIL, TR>(t_s, s_q, kt, idesc_qk, false);
+          tc_commit(bar(TR::kBarSFull));
+          issue_qk<TAIL, TR>(t_ds, s_q + TR::kTileBytes, kt, idesc_qk, false);
+          issue_qk<TAIL, TR>(t_ds, s_q, kt + TR::kTileBytes, idesc_qk, true);
+          tc_commit(bar(TR::kBarDSFull));
+          tc_commit(bar(TR::kBarKEmpty + sk));
+          ++kcnt;
+          if (num_kv_blocks == 1) tc_commit(bar(TR::kBarQEmpty));
+          for (int j = 0; j < num_kv_blocks; ++j) {
+            const uint32_t sv = vcnt % TR::kStagesV_;
+            const uint32_t vt = s_v + sv * TR::kGroupBytes;
+            ok = wait(TR::kBarVFull + sv, (vcnt / TR::kStagesV_) & 1u);
+            if (!ok) break;
+            ok = wait(TR::kBarPFull, pcnt & 1u);
+            if (!ok) break;
+            ++pcnt;
+            tc_fence_after_sync();
+            issue_pv<TAIL, TR>(t_o, t_s, vt, idesc_pv_main, idesc_pv_tail, j > 0);                  // O += P V
+            issue_pv<TAIL, TR>(t_t, t_s, vt + TR::kTileBytes, idesc_pv_main, idesc_pv_tail, j > 0); // T += P dV
+            const bool more = (j + 1 < num_kv_blocks);
+            if (more) {
+              sk = kcnt % TR::kStagesK_;
+              ok = wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK_) & 1u);
+              if (!ok) break;
+              tc_fence_after_sync();
+              kt = s_k + sk * TR::kGroupBytes;
+              issue_qk<TAIL, TR>(t_s, s_q, kt, idesc_qk, false);  // S of the next block (over P: issued after its readers)
+              tc_commit(bar(TR::kBarSFull));
+            }
+            ok = wait(TR::kBarGFull, gcnt & 1u);
+            if (!ok) break;
+            ++gcnt;
+            tc_fence_after_sync();
+            issue_pv<TAIL, TR>(t_t, t_ds, vt, idesc_pv_main, idesc_pv_tail, true);  // T += G V
+            tc_commit(bar(TR::kBarAccFull));
+            tc_commit(bar(TR::kBarVEmpty + sv));
+            ++vcnt;
+            if (more) {
+              issue_qk<TAIL, TR>(t_ds, s_q + TR::kTileBytes, kt, idesc_qk, false);
+              issue_qk<TAIL, TR>(t_ds, s_q, kt + TR::kTileBytes, idesc_qk, true);
+              tc_commit(bar(TR::kBarDSFull));
+              tc_commit(bar(TR::kBarKEmpty + sk));
+              ++kcnt;
+              if (j + 2 == num_kv_blocks) tc_commit(bar(TR::kBarQEmpty));
+            }
+          }
+        } else {
+          // plain forward: S double-buffered in the S / dS columns
+          auto issue_s = [&]() -> bool {
+            const uint32_t sk = kcnt % TR::kStagesK_;
+            if (!wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK_) & 1u)) return false;
+            tc_fence_after_sync();
+            issue_qk<TAIL, TR>((scnt & 1u) ? t_ds : t_s, s_q, s_k + sk * TR::kGroupBytes, idesc_qk, false);
+            tc_commit(bar(TR::kBarSFull));
+            tc_commit(bar(TR::kBarKEmpty + sk));
+            ++kcnt;
+            ++scnt;
+            return true;
+          };
+          ok = issue_s();
+          if (!ok) break;
+          if (num_kv_blocks == 1) tc_commit(bar(TR::kBarQEmpty));
+          for (int j = 0; j < num_kv_blocks; ++j) {
+            if (j + 1 < num_kv_blocks) {
+              ok = issue_s();
+              if (!ok) break;
+              if (j + 2 == num_kv_blocks) tc_commit(bar(TR::kBarQEmpty));
+            }
+            const uint32_t sv = vcnt % TR::kStagesV_;
+            ok = wait(TR::kBarVFull + sv, (vcnt / TR::kStagesV_) & 1u);
+            if (!ok) break;
+            ok = wait(TR::kBarPFull, pcnt & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_pv<TAIL, TR>(t_o, (pcnt & 1u) ? t_ds : t_s, s_v + sv * TR::kGroupBytes, idesc_pv_main,
+                               idesc_pv_tail, j > 0);
+            ++pcnt;
+            tc_commit(bar(TR::kBarAccFull));
+            tc_commit(bar(TR::kBarVEmpty + sv));
+            ++vcnt;
+          }
+        }
+      }
+    }
+  } else {
+    // ===================== softmax / correction / epilogue ==================
+    const int quarter = warp & 3;               // tensor-memory lane quarter this warp may touch
+    const int row = quarter * 32 + lane;        // query row inside the tile
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + TR::kColS, t_ds = tmem + lane_base + TR::kColDS;
+    const uint32_t t_o = tmem + lane_base + TR::kColO;
+    const float sl2 = p.scale_log2e;
+    uint32_t gblk = 0;  // blocks processed so far by this CTA (all tiles)
+    bool ok = true;
+    // warp-uniform result: the warp-wide votes and .sync.aligned instructions below need all 32 lanes
+    auto wait = [&](int b_, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleSoftmax + b_));
+    };
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      const int bh = tile / p.num_q_tiles;
+      const int q0 = (tile % p.num_q_tiles) * kBlockQ;
+      const int b = bh / p.heads, h = bh % p.heads;
+      float m_used = -CUDART_INF_F, l = 0.f, mu = 0.f;
+      for (int j = 0; j < num_kv_blocks; ++j, ++gblk) {
+        // ---- part 1: S -> P ------------------------------------------------
+        ok = wait(TR::kBarSFull, gblk & 1u);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t t_sb = (!kDual && (gblk & 1u)) ? t_ds : t_s;
+        uint32_t r[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_x32(t_sb + c * 32, r[c]);
+        tmem_wait_ld();
+        float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(r[c][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(r[c][i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(r[c][i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(r[c][i + 3]));
+          }
+        }
+        const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+        if (j == 0) {
+          m_used = m_blk;
+        } else {
+          const bool need = m_blk > m_used + kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            // every MMA that accumulates into O / T for the previous blocks must be done
+            ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const float alpha = need ? fast_exp2(m_used - m_blk) : 1.f;
+            if (need) m_used = m_blk;
+            l *= alpha;
+            mu *= alpha;
+            constexpr int kAccCols = kDual ? 2 * DPAD : DPAD;
+#pragma unroll 1
+            for (int c = 0; c < kAccCols / 16; ++c) {
+              uint32_t a[16];
+              tmem_ld_x16(t_o + c * 16, a);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) * alpha);
+              tmem_st_x16(t_o + c * 16, a);
+            }
+            tmem_wait_st();
+          }
+        }
+        const float neg_m = -m_used;
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(r[c][i]), sl2, neg_m));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(r[c][i + 1]), sl2, neg_m));
+            const float p2 = fast_exp2(fmaf(__uint_as_float(r[c][i + 2]), sl2, neg_m));
+            const float p3 = fast_exp2(fmaf(__uint_as_float(r[c][i + 3]), sl2, neg_m));
+            l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+            r[c][i] = __float_as_uint(p0);
+            r[c][i + 1] = __float_as_uint(p1);
+            r[c][i + 2] = __float_as_uint(p2);
+            r[c][i + 3] = __float_as_uint(p3);
+          }
+        }
+        l += (l0 + l1) + (l2 + l3);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pk[i] = Pack2<T>::pack(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
+          tmem_st_x16(t_sb + c * 16, pk);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar(TR::kBarPFull));
+
+        if constexpr (kDual) {
+          // ---- part 2: G = P * dS * scale, mu += rowsum(G) ------------------
+          ok = wait(TR::kBarDSFull, gblk & 1u);
+          if (!ok) break;
+          tc_fence_after_sync();
+          float mu0 = 0.f, mu1 = 0.f;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t d[32];
+            tmem_ld_x32(t_ds + c * 32, d);
+            tmem_wait_ld();
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float g0 = __uint_as_float(r[c][2 * i]) * (__uint_as_float(d[2 * i]) * p.scale);
+              const float g1 = __uint_as_float(r[c][2 * i + 1]) * (__uint_as_float(d[2 * i + 1]) * p.scale);
+              mu0 += g0;
+              mu1 += g1;
+              pk[i] = Pack2<T>::pack(g0, g1);
+            }
+            tmem_st_x16(t_ds + c * 16, pk);
+          }
+          mu += mu0 + mu1;
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(bar(TR::kBarGFull));
+        }
+      }
+      if (!ok) break;
+      // ---- epilogue: normalise and write o, to, lse -------------------------
+      ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const float inv_l = 1.f / l;
+      const float mu_n = mu * inv_l;
+      const int64_t lq = q0 + row;
+      T* o_row = reinterpret_cast<T*>(p.o) + b * p.o_sb + lq * p.o_sl + h * p.o_sh;
+      T* to_row = kDual ? reinterpret_cast<T*>(p.to) + b * p.to_sb + lq * p.to_sl + h * p.to_sh : nullptr;
+#pragma unroll
+      for (int c = 0; c < DPAD / 16; ++c) {
+        uint32_t a[16], t[16];
+        tmem_ld_x16(t_o + c * 16, a);
+        if constexpr (kDual) tmem_ld_x16(t_o + DPAD + c * 16, t);
+        tmem_wait_ld();
+        uint32_t po[8], pt[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float o0 = __uint_as_float(a[2 * i]) * inv_l;
+          const float o1 = __uint_as_float(a[2 * i + 1]) * inv_l;
+          po[i] = Pack2<T>::pack(o0, o1);
+          if constexpr (kDual) {
+            const float t0 = fmaf(__uint_as_float(t[2 * i]), inv_l, -mu_n * o0);
+            const float t1 = fmaf(__uint_as_float(t[2 * i + 1]), inv_l, -mu_n * o1);
+            pt[i] = Pack2<T>::pack(t0, t1);
+          }
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int col0 = c * 16 + hh * 8;
+          if (col0 < p.head_dim) {
+            *reinterpret_cast<uint4*>(o_row + col0) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
+            if constexpr (kDual)
+              *reinterpret_cast<uint4*>(to_row + col0) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
+          }
+        }
+      }
+      p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seqlen_q + lq] =
+          (m_used + __log2f(l)) * 0.6931471805599453f;
+      // the accumulator reads above must be complete before the next tile's first MMA overwrites O / T
+      tc_fence_before_sync();
+    }
+  }
+
+  // ============================== teardown ==================================
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 0) tmem_dealloc(tmem, TR::kTmemCols);
+}
+
+}  // namespace dmf

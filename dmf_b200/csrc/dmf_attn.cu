@@ -1,0 +1,310 @@
+// Host side of the C ABI declared in include/dmf_attn.h: argument validation,
+// TMA tensor-map construction and kernel launches.  No torch types, no device
+// allocation, no global mutable state besides per-device cached attributes.
+#include "dmf_attn.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstring>
+
+#include "attn_fwd.cuh"
+
+namespace {
+
+using namespace dmf;
+
+// ---- driver entry point for tensor-map encoding (no link-time libcuda dependency) ----
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static std::atomic<EncodeTiledFn> cached{nullptr};
+  EncodeTiledFn fn = cached.load(std::memory_order_acquire);
+  if (fn != nullptr) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || sym == nullptr) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  cached.store(fn, std::memory_order_release);
+  return fn;
+}
+
+// ---- per-device attributes ----
+
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  std::atomic<int> ready{0};
+  int sm_count = 0;
+  int cc_major = 0;
+};
+DeviceInfo g_devices[kMaxDevices];
+
+int device_info(int* sm_count) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_DEVICE;
+  }
+  DeviceInfo& d = g_devices[dev];
+  if (d.ready.load(std::memory_order_acquire) == 0) {
+    int sms = 0, major = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return DMF_ATTN_ERR_DEVICE;
+    }
+    d.sm_count = sms;
+    d.cc_major = major;
+    d.ready.store(1, std::memory_order_release);
+  }
+  if (d.cc_major != 10) return DMF_ATTN_ERR_DEVICE;
+  *sm_count = d.sm_count;
+  return DMF_ATTN_OK;
+}
+
+// ---- validation ----
+
+inline int tail_of(int d) {
+  if (d == 64) return 0;
+  if (d > 64 && d <= 80) return 16;
+  if (d > 80 && d <= 96) return 32;
+  if (d > 96 && d <= 128) return 64;
+  return -1;
+}
+
+inline int check_tensor(const dmf_attn_tensor& t, int elem_bytes) {
+  if (t.ptr == nullptr) return DMF_ATTN_ERR_NULL;
+  if ((reinterpret_cast<uintptr_t>(t.ptr) & 15u) != 0) return DMF_ATTN_ERR_ALIGN;
+  const int64_t s[3] = {t.stride_b, t.stride_l, t.stride_h};
+  for (int i = 0; i < 3; ++i) {
+    if (s[i] < 0) return DMF_ATTN_ERR_STRIDE;
+    if ((s[i] * elem_bytes) % 16 != 0) return DMF_ATTN_ERR_STRIDE;
+  }
+  return DMF_ATTN_OK;
+}
+
+inline int check_dims(int batch, int lq, int lkv, int heads, int d, int dtype) {
+  if (dtype != DMF_ATTN_BF16 && dtype != DMF_ATTN_FP16) return DMF_ATTN_ERR_DTYPE;
+  if (d < 64 || d > 128 || (d % 8) != 0) return DMF_ATTN_ERR_HEAD_DIM;
+  if (batch < 1 || heads < 1) return DMF_ATTN_ERR_SHAPE;
+  if (lq < kBlockQ || lkv < kBlockKV || (lq % kBlockQ) != 0 || (lkv % kBlockKV) != 0) return DMF_ATTN_ERR_SEQLEN;
+  if (static_cast<int64_t>(batch) * heads * (lq / kBlockQ) > 0x7fffffffll) return DMF_ATTN_ERR_SHAPE;
+  return DMF_ATTN_OK;
+}
+
+int validate_fwd(const dmf_attn_fwd_args* a, bool dual) {
+  if (a == nullptr) return DMF_ATTN_ERR_NULL;
+  int st = check_dims(a->batch, a->seqlen_q, a->seqlen_kv, a->heads, a->head_dim, a->dtype);
+  if (st != DMF_ATTN_OK) return st;
+  if (a->lse == nullptr) return DMF_ATTN_ERR_NULL;
+  if (!std::isfinite(a->softmax_scale)) return DMF_ATTN_ERR_SHAPE;
+  const dmf_attn_tensor* prim[] = {&a->q, &a->k, &a->v, &a->o};
+  for (const dmf_attn_tensor* t : prim)
+    if ((st = check_tensor(*t, 2)) != DMF_ATTN_OK) return st;
+  if (dual) {
+    const dmf_attn_tensor* tang[] = {&a->tq, &a->tk, &a->tv, &a->to};
+    for (const dmf_attn_tensor* t : tang)
+      if ((st = check_tensor(*t, 2)) != DMF_ATTN_OK) return st;
+  }
+  return DMF_ATTN_OK;
+}
+
+// ---- tensor maps ----
+
+// Map of a (B, L, H, D) tensor seen as dims (D, L, H, B); box = box_d columns x box_l rows of one (b, h).
+int make_map(CUtensorMap* map, const dmf_attn_tensor& t, int dtype, int batch, int seqlen, int heads, int d,
+             int box_d, int box_l, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) return DMF_ATTN_ERR_DEVICE;
+  const cuuint64_t es = 2;
+  const cuuint64_t row_bytes = ((static_cast<cuuint64_t>(d) * es + 15) / 16) * 16;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(seqlen),
+                        static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  // a dimension of extent 1 may carry any stride in the caller's tensor; give the map a legal one
+  cuuint64_t strides[3] = {
+      seqlen > 1 ? static_cast<cuuint64_t>(t.stride_l) * es : row_bytes,
+      heads > 1 ? static_cast<cuuint64_t>(t.stride_h) * es : row_bytes,
+      batch > 1 ? static_cast<cuuint64_t>(t.stride_b) * es : row_bytes,
+  };
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] == 0 || (strides[i] % 16) != 0) return DMF_ATTN_ERR_STRIDE;
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(box_d), static_cast<cuuint32_t>(box_l), 1, 1};
+  cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt =
+      dtype == DMF_ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = encode(map, dt, 4, t.ptr, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DMF_ATTN_OK : DMF_ATTN_ERR_TENSOR_MAP;
+}
+
+inline CUtensorMapSwizzle tail_swizzle(int tail) {
+  return tail == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (tail == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+int make_map_pair(CUtensorMap* main_map, CUtensorMap* tail_map, const dmf_attn_tensor& t, int dtype, int batch,
+                  int seqlen, int heads, int d, int tail, int box_l) {
+  int st = make_map(main_map, t, dtype, batch, seqlen, heads, d, 64, box_l, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st != DMF_ATTN_OK) return st;
+  if (tail > 0) return make_map(tail_map, t, dtype, batch, seqlen, heads, d, tail, box_l, tail_swizzle(tail));
+  std::memset(tail_map, 0, sizeof(CUtensorMap));
+  return DMF_ATTN_OK;
+}
+
+// ---- forward launch ----
+
+template <typename T, int TAIL, bool kDual>
+int launch_fwd_inst(const FwdParams& p, int grid, cudaStream_t stream) {
+  using TR = FwdTraits<TAIL, kDual>;
+  auto kernel = attn_fwd_kernel<T, TAIL, kDual>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::kSmemBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_LAUNCH;
+  }
+  kernel<<<grid, kFwdThreads, TR::kSmemBytes, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
+}
+
+template <typename T, bool kDual>
+int launch_fwd_tail(const FwdParams& p, int tail, int grid, cudaStream_t stream) {
+  switch (tail) {
+    case 0: return launch_fwd_inst<T, 0, kDual>(p, grid, stream);
+    case 16: return launch_fwd_inst<T, 16, kDual>(p, grid, stream);
+    case 32: return launch_fwd_inst<T, 32, kDual>(p, grid, stream);
+    case 64: return launch_fwd_inst<T, 64, kDual>(p, grid, stream);
+    default: return DMF_ATTN_ERR_HEAD_DIM;
+  }
+}
+
+int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
+  int st = validate_fwd(a, dual);
+  if (st != DMF_ATTN_OK) return st;
+  int sm_count = 0;
+  if ((st = device_info(&sm_count)) != DMF_ATTN_OK) return st;
+
+  const int tail = tail_of(a->head_dim);
+  FwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  const int B = a->batch, H = a->heads, D = a->head_dim, Lq = a->seqlen_q, Lk = a->seqlen_kv, dt = a->dtype;
+  if ((st = make_map_pair(&p.q_main, &p.q_tail, a->q, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.k_main, &p.k_tail, a->k, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.v_main, &p.v_tail, a->v, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
+  if (dual) {
+    if ((st = make_map_pair(&p.tq_main, &p.tq_tail, a->tq, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
+    if ((st = make_map_pair(&p.tk_main, &p.tk_tail, a->tk, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
+    if ((st = make_map_pair(&p.tv_main, &p.tv_tail, a->tv, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
+  }
+  p.o = a->o.ptr;
+  p.o_sb = a->o.stride_b; p.o_sl = a->o.stride_l; p.o_sh = a->o.stride_h;
+  if (dual) {
+    p.to = a->to.ptr;
+    p.to_sb = a->to.stride_b; p.to_sl = a->to.stride_l; p.to_sh = a->to.stride_h;
+  }
+  p.lse = a->lse;
+  p.status_word = a->status_word;
+  p.batch = B; p.heads = H; p.seqlen_q = Lq; p.seqlen_kv = Lk; p.head_dim = D;
+  p.num_q_tiles = Lq / kBlockQ;
+  p.num_tiles = B * H * p.num_q_tiles;
+  p.scale = a->softmax_scale;
+  p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
+  const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (dt == DMF_ATTN_BF16)
+    return dual ? launch_fwd_tail<__nv_bfloat16, true>(p, tail, grid, stream)
+                : launch_fwd_tail<__nv_bfloat16, false>(p, tail, grid, stream);
+  return dual ? launch_fwd_tail<__half, true>(p, tail, grid, stream)
+              : launch_fwd_tail<__half, false>(p, tail, grid, stream);
+}
+
+// ---- backward ----
+
+size_t bwd_workspace_bytes(int batch, int lq, int lkv, int heads, int d) {
+  if (check_dims(batch, lq, lkv, heads, d, DMF_ATTN_BF16) != DMF_ATTN_OK) return 0;
+  return 0;
+}
+
+int validate_bwd(const dmf_attn_bwd_args* a) {
+  if (a == nullptr) return DMF_ATTN_ERR_NULL;
+  int st = check_dims(a->batch, a->seqlen_q, a->seqlen_kv, a->heads, a->head_dim, a->dtype);
+  if (st != DMF_ATTN_OK) return st;
+  if (a->lse == nullptr) return DMF_ATTN_ERR_NULL;
+  if (!std::isfinite(a->softmax_scale)) return DMF_ATTN_ERR_SHAPE;
+  const dmf_attn_tensor* ts[] = {&a->dout, &a->q, &a->k, &a->v, &a->o, &a->dq, &a->dk, &a->dv};
+  for (const dmf_attn_tensor* t : ts)
+    if ((st = check_tensor(*t, 2)) != DMF_ATTN_OK) return st;
+  const size_t need = bwd_workspace_bytes(a->batch, a->seqlen_q, a->seqlen_kv, a->heads, a->head_dim);
+  if (need > 0 && (a->workspace == nullptr || a->workspace_bytes < need)) return DMF_ATTN_ERR_WORKSPACE;
+  return DMF_ATTN_OK;
+}
+
+int run_bwd(const dmf_attn_bwd_args* a) {
+  int st = validate_bwd(a);
+  if (st != DMF_ATTN_OK) return st;
+  return DMF_ATTN_ERR_LAUNCH;
+}
+
+}  // namespace
+
+#define DMF_API __attribute__((visibility("default")))
+
+extern "C" {
+
+DMF_API int dmf_attn_abi_version(void) { return DMF_ATTN_ABI_VERSION; }
+
+DMF_API const char* dmf_attn_status_string(int status) {
+  switch (status) {
+    case DMF_ATTN_OK: return "ok";
+    case DMF_ATTN_ERR_NULL: return "a required pointer is NULL";
+    case DMF_ATTN_ERR_DTYPE: return "unsupported dtype (bf16 and fp16 only)";
+    case DMF_ATTN_ERR_HEAD_DIM: return "unsupported head_dim (multiples of 8 in [64, 128])";
+    case DMF_ATTN_ERR_SEQLEN: return "seqlen_q and seqlen_kv must be positive multiples of 128";
+    case DMF_ATTN_ERR_SHAPE: return "bad batch / heads / scale";
+    case DMF_ATTN_ERR_STRIDE: return "strides must be non-negative and a multiple of 16 bytes";
+    case DMF_ATTN_ERR_ALIGN: return "base pointers must be 16-byte aligned";
+    case DMF_ATTN_ERR_DEVICE: return "no usable sm_100 CUDA device";
+    case DMF_ATTN_ERR_TENSOR_MAP: return "the driver rejected a TMA tensor map";
+    case DMF_ATTN_ERR_LAUNCH: return "kernel launch failed";
+    case DMF_ATTN_ERR_WORKSPACE: return "workspace missing or too small";
+    case DMF_ATTN_ERR_TIMEOUT: return "a device-side wait ran out";
+    default: return "unknown status";
+  }
+}
+
+DMF_API int dmf_attn_fwd_dual(const dmf_attn_fwd_args* args) { return run_fwd(args, true); }
+
+DMF_API int dmf_attn_fwd(const dmf_attn_fwd_args* args) { return run_fwd(args, false); }
+
+DMF_API int dmf_attn_validate_fwd(const dmf_attn_fwd_args* args, int dual) { return validate_fwd(args, dual != 0); }
+
+DMF_API int dmf_attn_validate_bwd(const dmf_attn_bwd_args* args) { return validate_bwd(args); }
+
+DMF_API size_t dmf_attn_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t seqlen_kv, int32_t heads,
+                                    int32_t head_dim) {
+  return bwd_workspace_bytes(batch, seqlen_q, seqlen_kv, heads, head_dim);
+}
+
+DMF_API int dmf_attn_bwd(const dmf_attn_bwd_args* args) { return run_bwd(args); }
+
+DMF_API int dmf_attn_check_status_word(const int32_t* status_word, void* stream, int32_t* raw) {
+  if (status_word == nullptr) return DMF_ATTN_ERR_NULL;
+  int32_t host = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(&host, status_word, sizeof(host), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_DEVICE;
+  }
+  if (raw != nullptr) *raw = host;
+  return host == 0 ? DMF_ATTN_OK : DMF_ATTN_ERR_TIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,165 @@
+/*
+ * dmf_attn.h - C ABI of the B200 (sm_100a) attention kernels behind
+ * Decoupled MeanFlow's flash_attn_func.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, never
+ * allocates or frees device memory, never keeps a pointer after it returns and
+ * launches asynchronously on the CUDA stream it is given.  All tensors use the
+ * reference layout (B, L, H, D) with an arbitrary element stride for B, L and H
+ * and stride 1 for D, so the strided q/k/v views of a packed qkv projection are
+ * consumed without a copy.
+ *
+ * Return value: 0 (DMF_ATTN_OK) or one of the DMF_ATTN_ERR_* codes below; the
+ * text for a code comes from dmf_attn_status_string().  There is no CPU path:
+ * on a machine without an sm_100 device the compute entry points return
+ * DMF_ATTN_ERR_DEVICE.
+ */
+#ifndef DMF_ATTN_H_
+#define DMF_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DMF_ATTN_ABI_VERSION 1
+
+enum dmf_attn_dtype {
+  DMF_ATTN_BF16 = 0,
+  DMF_ATTN_FP16 = 1
+};
+
+enum dmf_attn_status {
+  DMF_ATTN_OK = 0,
+  DMF_ATTN_ERR_NULL = 1,        /* a required pointer is NULL                                  */
+  DMF_ATTN_ERR_DTYPE = 2,       /* dtype is not bf16 / fp16                                    */
+  DMF_ATTN_ERR_HEAD_DIM = 3,    /* head_dim not in {64, 72, 80, 88, 96, 104, ..., 128}         */
+  DMF_ATTN_ERR_SEQLEN = 4,      /* seqlen_q or seqlen_kv is not a positive multiple of 128     */
+  DMF_ATTN_ERR_SHAPE = 5,       /* batch or heads < 1, or a size overflows                     */
+  DMF_ATTN_ERR_STRIDE = 6,      /* a stride (in bytes) is not a multiple of 16                 */
+  DMF_ATTN_ERR_ALIGN = 7,       /* a base pointer is not 16-byte aligned                       */
+  DMF_ATTN_ERR_DEVICE = 8,      /* no CUDA device, or the device is not compute capability 10.x */
+  DMF_ATTN_ERR_TENSOR_MAP = 9,  /* the driver rejected a TMA tensor map                        */
+  DMF_ATTN_ERR_LAUNCH = 10,     /* the kernel launch failed (see cudaGetLastError)             */
+  DMF_ATTN_ERR_WORKSPACE = 11,  /* workspace missing or too small                              */
+  DMF_ATTN_ERR_TIMEOUT = 12     /* a device-side wait ran out (reported by dmf_attn_check_status_word) */
+};
+
+/* One (B, L, H, D) tensor: base pointer and element strides; the D stride is 1. */
+typedef struct dmf_attn_tensor {
+  void* ptr;
+  int64_t stride_b;
+  int64_t stride_l;
+  int64_t stride_h;
+} dmf_attn_tensor;
+
+/*
+ * Arguments of the forward kernels.
+ *
+ * status_word (optional, may be NULL): one int32 in device memory, zeroed by
+ * the caller.  Every device-side wait has an upper limit; a kernel whose wait
+ * runs out writes a non-zero code there, releases what it holds and returns
+ * normally, so the CUDA context stays usable.  Read it back with
+ * dmf_attn_check_status_word().
+ */
+typedef struct dmf_attn_fwd_args {
+  int32_t batch;
+  int32_t seqlen_q;
+  int32_t seqlen_kv;
+  int32_t heads;
+  int32_t head_dim;
+  int32_t dtype;            /* enum dmf_attn_dtype                                   */
+  float softmax_scale;      /* applied to Q K^T; the reference default is D^-0.5     */
+  int32_t reserved;
+  dmf_attn_tensor q, k, v;  /* primals, read only                                    */
+  dmf_attn_tensor tq, tk, tv; /* tangents, read only (ignored by dmf_attn_fwd)       */
+  dmf_attn_tensor o;        /* out: softmax(s Q K^T) V                               */
+  dmf_attn_tensor to;       /* out: tangent of o (ignored by dmf_attn_fwd)           */
+  float* lse;               /* out: (B, H, Lq) contiguous fp32, natural-log LSE of s Q K^T */
+  int32_t* status_word;     /* optional device int32, see above                      */
+  void* stream;             /* cudaStream_t                                          */
+} dmf_attn_fwd_args;
+
+/*
+ * Arguments of the primal backward.  grads of lse and of the tangent output are
+ * not inputs: the reference drops them (stop-gradient on the tangent).
+ * workspace: device memory of at least dmf_attn_bwd_workspace_bytes(); its
+ * contents on entry do not matter (the call clears what it accumulates into).
+ */
+typedef struct dmf_attn_bwd_args {
+  int32_t batch;
+  int32_t seqlen_q;
+  int32_t seqlen_kv;
+  int32_t heads;
+  int32_t head_dim;
+  int32_t dtype;
+  float softmax_scale;
+  int32_t reserved;
+  dmf_attn_tensor dout;     /* grad of o, read only                                  */
+  dmf_attn_tensor q, k, v;  /* saved primals                                         */
+  dmf_attn_tensor o;        /* saved output                                          */
+  const float* lse;         /* saved (B, H, Lq) fp32 LSE                             */
+  dmf_attn_tensor dq, dk, dv; /* out                                                 */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status_word;
+  void* stream;
+} dmf_attn_bwd_args;
+
+/* ABI version of the loaded library (DMF_ATTN_ABI_VERSION it was built with). */
+int dmf_attn_abi_version(void);
+
+/* Static, NUL-terminated description of a status code. */
+const char* dmf_attn_status_string(int status);
+
+/*
+ * Fused forward + tangent ("dual" forward): o, to and lse from q, k, v and
+ * their tangents in one online-softmax pass.
+ * Replaces the Triton launches _attn_fwd_dual / _attn_fwd_dual_split made by
+ * FlashAttnFunc.forward (models/flash_attention_2_jvp.py:186-230,
+ * models/flash_attention_3_jvp.py:171-215; kernels models/triton_utils.py:258-500).
+ */
+int dmf_attn_fwd_dual(const dmf_attn_fwd_args* args);
+
+/*
+ * Plain forward: o and lse from q, k, v (no dropout, non-causal, no window).
+ * Replaces flash_attn_2_cuda.fwd (models/flash_attention_2_jvp.py:47-61) and
+ * torch.ops.flash_attn_3.fwd (models/flash_attention_3_jvp.py:72-107) as called
+ * from the non-dual branch of FlashAttnFunc.forward
+ * (models/flash_attention_2_jvp.py:231-243).
+ */
+int dmf_attn_fwd(const dmf_attn_fwd_args* args);
+
+/*
+ * Primal backward: dq, dk, dv from dout, q, k, v, o, lse.
+ * Replaces flash_attn_2_cuda.bwd (models/flash_attention_2_jvp.py:119-139) and
+ * torch.ops.flash_attn_3.bwd (models/flash_attention_3_jvp.py:136-159) as called
+ * from FlashAttnFunc.backward (models/flash_attention_2_jvp.py:260-276).
+ */
+int dmf_attn_bwd(const dmf_attn_bwd_args* args);
+
+/* Bytes of workspace dmf_attn_bwd needs for this problem size (0 on bad sizes). */
+size_t dmf_attn_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t seqlen_kv,
+                                    int32_t heads, int32_t head_dim);
+
+/*
+ * Copy a status word back (synchronises the stream) and translate it:
+ * DMF_ATTN_OK if it is zero, DMF_ATTN_ERR_TIMEOUT otherwise; *raw (optional)
+ * receives the word itself (which wait gave up).
+ */
+int dmf_attn_check_status_word(const int32_t* status_word, void* stream, int32_t* raw);
+
+/*
+ * Argument validation only (no device work): the status the compute entry
+ * points would return for these arguments before touching the GPU.
+ */
+int dmf_attn_validate_fwd(const dmf_attn_fwd_args* args, int dual);
+int dmf_attn_validate_bwd(const dmf_attn_bwd_args* args);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DMF_ATTN_H_ */
