@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the attention forward + tangent (JVP) hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload C3|C2]
+
+A step is one fused forward+tangent pass over one batch of seeded synthetic
+tensors with the shapes of the named configuration (default C3: SiT-XL/2 512px,
+B=64, H=16, N=1024, D=72, q/k RMS-normalised, tangents N(0,1)*0.1).  One process
+per GPU; with N > 1 (launched by torch.distributed.run) every rank runs the same
+per-GPU workload on its own batch shard - the op has no collective - and the
+reported value is the units all ranks processed divided by the slowest rank's
+device time ("weak" scaling).
+
+Rank 0 prints ONE JSON line.  `value` is kernel throughput with inputs resident in
+HBM; `e2e` is the same metric through the public API (flash_attn_func under
+torch.func.jvp) with pinned host buffers, host<->device copies inside the timed
+region; `roofline` relates the kernel to the measured bf16 peak; `cpu_baseline`
+is the CPU oracle (the reference's 'base' attention under torch.func.jvp, fp32)
+timed on this host on a bounded sample.
+
+--impl reference times that CPU path alone (all host threads), on the same
+metric and config, each step a bounded sample of the workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "attn_jvp_fwd_tangent_tflops"
+UNIT = "TFLOP/s"
+
+WORKLOADS = {
+    # name: (B, L, H, D, tangent_scale, qk_norm, description)
+    "C3": (64, 1024, 16, 72, 0.1, True, "attention JVP fwd+tangent, SiT-XL/2 512px: B=64 H=16 N=1024 D=72, qk-norm"),
+    "C2": (256, 256, 16, 72, 0.1, False, "attention JVP fwd+tangent, SiT-XL/2 256px: B=256 H=16 N=256 D=72"),
+}
+CPU_SAMPLE_BATCH = 2  # batch slice of the workload one CPU step computes
+
+
+def _flops(B, L, H, D):
+    return 12.0 * B * H * L * L * D
+
+
+def _algo_bytes(B, L, H, D):
+    return 16.0 * B * L * H * D + 4.0 * B * H * L
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"tflops": float(d["bf16_tflops"]), "tflops_sustained": float(d.get("bf16_tflops_sustained", 0.0)),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def _traffic(workload):
+    """DRAM bytes per launch from the committed ncu capture of this kernel, or None."""
+    p = ROOT / "profiles" / "dram_traffic.json"
+    if p.exists():
+        return json.loads(p.read_text()).get(workload, {}).get("dram_bytes_per_launch")
+    return None
+
+
+class ClockSampler(threading.Thread):
+    """Reads (never sets) SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.active = threading.Event()
+        self.error = None
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+                "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+            }
+            while not self._stop_evt.is_set():
+                if self.active.is_set():
+                    self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    for k, bit in names.items():
+                        if mask & bit:
+                            self.reasons.add(k)
+                time.sleep(self.period)
+        except Exception as e:  # NVML missing: report, do not fail the bench
+            self.error = repr(e)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s), **({"error": self.error} if self.error else {})}
+
+
+def _cpu_step_fn(workload, batch):
+    """The CPU oracle on a batch slice of the workload; returns (callable, flops per call)."""
+    import torch
+    from oracle import attn_jvp_oracle as orc
+    B, L, H, D, ts, qkn, _ = WORKLOADS[workload]
+    ins = orc.make_inputs(batch, L, H, D, seed=0, tangent_scale=ts, qk_norm=qkn)
+
+    def step():
+        with torch.no_grad():
+            return orc.attn_jvp_base(*ins)
+
+    return step, _flops(batch, L, H, D)
+
+
+def _time_cpu(step, n_steps, warmup):
+    for _ in range(warmup):
+        step()
+    ts = []
+    for _ in range(n_steps):
+        t0 = time.perf_counter()
+        step()
+        ts.append(time.perf_counter() - t0)
+    return ts
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path (oracle port), all host threads, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    B, L, H, D, ts, qkn, desc = WORKLOADS[args.workload]
+    step, fl = _cpu_step_fn(args.workload, CPU_SAMPLE_BATCH)
+    times = _time_cpu(step, args.steps, args.warmup)
+    total = sum(times)
+    value = fl * len(times) / total / 1e12
+    sample = (f"batch slice B={CPU_SAMPLE_BATCH} of {args.workload} per step ({fl / 1e9:.1f} GFLOP), fp32, "
+              f"'base' attention under torch.func.jvp")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {desc}", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the sm_100a kernels have no CPU path "
+                         "(use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from dmf_b200 import flash_attn_func, ops
+    from oracle import attn_jvp_oracle as orc  # cpu_baseline leg only
+
+    B, L, H, D, ts, qkn, desc = WORKLOADS[args.workload]
+    if args.batch is not None:
+        B, desc = args.batch, desc + f" [batch overridden to {args.batch}: not a bench line]"
+    scale = D ** -0.5
+    # seeded synthetic inputs, per-rank shard of the data-parallel batch (seed = rank)
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    qkv = torch.randn(B, L, 3, H, D, device=dev, dtype=torch.float32, generator=gen)
+    tqkv = torch.randn(B, L, 3, H, D, device=dev, dtype=torch.float32, generator=gen) * ts
+    if qkn:
+        # per-head RMSNorm of q, k and the matching tangents (weight = 1, eps = 1e-6)
+        def norm_jvp(x, tx):
+            r = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+            return x * r, tx * r - x * r.pow(3) * (x * tx).mean(-1, keepdim=True)
+        q, tq = norm_jvp(qkv[:, :, 0], tqkv[:, :, 0])
+        k, tk = norm_jvp(qkv[:, :, 1], tqkv[:, :, 1])
+        q, k, tq, tk = (x.to(torch.bfloat16).contiguous() for x in (q, k, tq, tk))
+    else:
+        qkv16, tqkv16 = qkv.to(torch.bfloat16), tqkv.to(torch.bfloat16)
+        q, k, tq, tk = qkv16[:, :, 0], qkv16[:, :, 1], tqkv16[:, :, 0], tqkv16[:, :, 1]
+    v = qkv.to(torch.bfloat16)[:, :, 2]
+    tv = tqkv.to(torch.bfloat16)[:, :, 2]
+    del qkv, tqkv
+    ins = (q, k, v, tq, tk, tv)
+
+    def step():
+        return ops.fwd_dual_raw(*ins, scale)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    sync_all()
+
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
+    sampler.start()
+    stream = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    sampler.active.set()
+    e0.record(stream)
+    for _ in range(args.steps):
+        out = step()
+    e1.record(stream)
+    sync_all()
+    sampler.active.clear()
+    ms_total = e0.elapsed_time(e1)
+    ops.check_device_status(dev)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    fl = _flops(B, L, H, D)
+    value = world * fl / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public API, host buffers, copies inside the timed region ----
+    e2e_steps = max(1, min(args.steps, 10))
+    if args.no_e2e:
+        e2e_steps = 0
+    host_in = [x.contiguous().cpu().pin_memory() for x in ins]
+    dev_in = [torch.empty_like(x, device=dev) for x in host_in]
+    host_out = [torch.empty((B, L, H, D), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+
+    def e2e_step():
+        for h, d in zip(host_in, dev_in):
+            d.copy_(h, non_blocking=True)
+        o, do = torch.func.jvp(lambda a, b, c: flash_attn_func(a, b, c), tuple(dev_in[:3]), tuple(dev_in[3:]))
+        host_out[0].copy_(o, non_blocking=True)
+        host_out[1].copy_(do, non_blocking=True)
+
+    for _ in range(2 if e2e_steps else 0):
+        e2e_step()
+    sync_all()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    sync_all()
+    sampler.stop()
+    e2e_ms = e0.elapsed_time(e1) if e2e_steps else float("nan")
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * fl * e2e_steps / (e2e_ms * 1e-3) / 1e12 if e2e_steps else None
+    h2d = sum(x.numel() * x.element_size() for x in host_in)
+    d2h = sum(x.numel() * x.element_size() for x in host_out)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = _peaks()
+    achieved = fl / (ms_step * 1e-3) / 1e12  # per launch, per GPU
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+        "frac": achieved / peaks["tflops"], "traffic": _traffic(args.workload),
+        "peak_source": f"bf16 burst, of {peaks['source']}",
+        "frac_of_sustained": (achieved / peaks["tflops_sustained"]) if peaks["tflops_sustained"] else None,
+        "frac_of_nominal_2250": achieved / 2250.0,
+        "algorithmic_flops_per_launch": fl, "algorithmic_bytes_per_launch": _algo_bytes(B, L, H, D),
+        "hbm_gbs_achieved": _algo_bytes(B, L, H, D) / (ms_step * 1e-3) / 1e9,
+        "kernel": "attn_fwd_kernel<bf16, TAIL=16, dual>",
+    }
+
+    cpu_base = None
+    if world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        cstep, cfl = _cpu_step_fn(args.workload, CPU_SAMPLE_BATCH)
+        t0 = time.perf_counter()
+        times = _time_cpu(cstep, 5, 1)
+        cpu_base = {
+            "value": cfl * len(times) / sum(times) / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"5 runs of a B={CPU_SAMPLE_BATCH} batch slice of {args.workload} ({cfl / 1e9:.1f} GFLOP each), "
+                      f"fp32 'base' attention under torch.func.jvp, {time.perf_counter() - t0:.1f} s of CPU work",
+        }
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {desc}", "per_gpu_batch": B,
+                   "l2": "inputs (906 MB per GPU) are larger than the 126 MB L2; no flush between steps",
+                   "layout": "q,k contiguous after qk-norm; v and tangents strided views of packed qkv"
+                             if qkn else "strided views of packed qkv"},
+        "roofline": roofline,
+        "cpu_baseline": cpu_base,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps, "ms_per_step": (e2e_ms / e2e_steps) if e2e_steps else None,
+                "api": "torch.func.jvp(dmf_b200.flash_attn_func) on pinned host tensors"},
+        "gpu_launches": args.steps,
+        "clocks": sampler.summary(),
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=list(WORKLOADS), default="C3")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="override the per-GPU batch of the workload (profiling runs only; the bench line needs the default)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

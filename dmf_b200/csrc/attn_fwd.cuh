@@ -77,7 +77,7 @@ struct FwdTraits {
   static constexpr int kTileSmem = kGroupBytes * (1 + kStagesK_ + kStagesV_);
   // barriers
   static constexpr int kBarQFull = 0, kBarQEmpty = 1, kBarSFull = 2, kBarDSFull = 3, kBarPFull = 4,
-                       kBarGFull = 5, kBarAccFull = 6, kBarKFull = 7,
+                       kBarGFull = 5, kBarAccFull = 6 /* and 7 */, kBarKFull = 8,
                        kBarKEmpty = kBarKFull + kStagesK_, kBarVFull = kBarKEmpty + kStagesK_,
                        kBarVEmpty = kBarVFull + kStagesV_, kNumBars = kBarVEmpty + kStagesV_;
   static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kTileSmem + kNumBars * 8 + 16;
@@ -157,7 +157,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < TR::kNumBars; ++i) {
-      const bool softmax_arrives = (i == TR::kBarPFull || i == TR::kBarGFull);
+      const bool softmax_arrives = (i == TR::kBarPFull || i == TR::kBarGFull);  // kBarGFull == kBarPFull + 1
       mbar_init(bar(i), softmax_arrives ? 128u : 1u);
     }
     fence_mbar_init();
@@ -303,13 +303,16 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             }
           }
         } else {
-          // plain forward: S double-buffered in the S / dS columns
+          // plain forward: S double-buffered in the S / dS columns.  Each buffer has its own
+          // "S ready" and "P ready" barrier (the dS / G barriers of the dual pass), because S of
+          // block g+1 is issued before P of block g is awaited: one barrier shared by both
+          // buffers could run two phases ahead of its waiter, which a parity wait cannot express.
           auto issue_s = [&]() -> bool {
             const uint32_t sk = kcnt % TR::kStagesK_;
             if (!wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK_) & 1u)) return false;
             tc_fence_after_sync();
             issue_qk<TAIL, TR>((scnt & 1u) ? t_ds : t_s, s_q, s_k + sk * TR::kGroupBytes, idesc_qk, false);
-            tc_commit(bar(TR::kBarSFull));
+            tc_commit(bar(TR::kBarSFull + (scnt & 1u)));
             tc_commit(bar(TR::kBarKEmpty + sk));
             ++kcnt;
             ++scnt;
@@ -327,13 +330,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             const uint32_t sv = vcnt % TR::kStagesV_;
             ok = wait(TR::kBarVFull + sv, (vcnt / TR::kStagesV_) & 1u);
             if (!ok) break;
-            ok = wait(TR::kBarPFull, pcnt & 1u);
+            ok = wait(TR::kBarPFull + (pcnt & 1u), (pcnt >> 1) & 1u);
             if (!ok) break;
             tc_fence_after_sync();
             issue_pv<TAIL, TR>(t_o, (pcnt & 1u) ? t_ds : t_s, s_v + sv * TR::kGroupBytes, idesc_pv_main,
                                idesc_pv_tail, j > 0);
+            tc_commit(bar(TR::kBarAccFull + (pcnt & 1u)));
             ++pcnt;
-            tc_commit(bar(TR::kBarAccFull));
             tc_commit(bar(TR::kBarVEmpty + sv));
             ++vcnt;
           }
@@ -354,6 +357,15 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     auto wait = [&](int b_, uint32_t parity) -> bool {
       return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleSoftmax + b_));
     };
+    // Wait until the MMAs that accumulate block `blk` into O / T are complete.  A parity wait
+    // only works while the barrier is at most one phase ahead of the waiter.  Dual pass: one
+    // barrier, one commit per block; by the time this is called for block c the commit of c-1
+    // is known complete (the dS of block c, awaited in part 2, was issued after it).  Plain
+    // pass: the softmax can run a block ahead of the P V products, so even and odd blocks
+    // commit to separate barriers; the commit of c-2 is complete once S of block c has arrived.
+    auto wait_acc = [&](uint32_t blk) -> bool {
+      return kDual ? wait(TR::kBarAccFull, blk & 1u) : wait(TR::kBarAccFull + (blk & 1u), (blk >> 1) & 1u);
+    };
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
       const int bh = tile / p.num_q_tiles;
       const int q0 = (tile % p.num_q_tiles) * kBlockQ;
@@ -361,10 +373,11 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       float m_used = -CUDART_INF_F, l = 0.f, mu = 0.f;
       for (int j = 0; j < num_kv_blocks; ++j, ++gblk) {
         // ---- part 1: S -> P ------------------------------------------------
-        ok = wait(TR::kBarSFull, gblk & 1u);
+        const uint32_t buf = kDual ? 0u : (gblk & 1u);
+        ok = wait(TR::kBarSFull + buf, kDual ? (gblk & 1u) : ((gblk >> 1) & 1u));
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t t_sb = (!kDual && (gblk & 1u)) ? t_ds : t_s;
+        const uint32_t t_sb = buf ? t_ds : t_s;
         uint32_t r[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld_x32(t_sb + c * 32, r[c]);
@@ -387,7 +400,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           const bool need = m_blk > m_used + kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
             // every MMA that accumulates into O / T for the previous blocks must be done
-            ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+            ok = wait_acc(gblk - 1u);
             if (!ok) break;
             tc_fence_after_sync();
             const float alpha = need ? fast_exp2(m_used - m_blk) : 1.f;
@@ -435,7 +448,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(bar(TR::kBarPFull));
+        mbar_arrive(bar(TR::kBarPFull + buf));
 
         if constexpr (kDual) {
           // ---- part 2: G = P * dS * scale, mu += rowsum(G) ------------------
@@ -467,7 +480,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       }
       if (!ok) break;
       // ---- epilogue: normalise and write o, to, lse -------------------------
-      ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+      ok = wait_acc(gblk - 1u);
       if (!ok) break;
       tc_fence_after_sync();
       const float inv_l = 1.f / l;

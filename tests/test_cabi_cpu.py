@@ -1,0 +1,108 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header
+declares, and rejects bad arguments with the documented status codes."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from dmf_b200 import _lib
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "dmf_attn.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dmf_attn_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_loads_and_exports_header_symbols():
+    lib = _lib.load()
+    declared = _declared_symbols()
+    assert set(declared) == set(_lib.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.dmf_attn_abi_version() == _lib.ABI_VERSION
+
+
+def test_status_strings():
+    lib = _lib.load()
+    seen = set()
+    for code in _lib.STATUS_NAMES:
+        s = lib.dmf_attn_status_string(code).decode()
+        assert s and s not in seen
+        seen.add(s)
+    assert lib.dmf_attn_status_string(999).decode() == "unknown status"
+
+
+def _good_args(dual=True):
+    a = _lib.FwdArgs()
+    a.batch, a.seqlen_q, a.seqlen_kv, a.heads, a.head_dim = 2, 256, 256, 4, 72
+    a.dtype, a.softmax_scale = _lib.BF16, 72 ** -0.5
+    fake = 0x10000  # never dereferenced by validation
+    for name in ("q", "k", "v", "tq", "tk", "tv", "o", "to"):
+        setattr(a, name, _lib.Tensor4(fake, 256 * 4 * 72, 4 * 72, 72))
+    a.lse = fake
+    return a
+
+
+def test_validation_accepts_reference_layouts():
+    lib = _lib.load()
+    a = _good_args()
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 1) == 0
+    # strided views of a packed (B, L, 3, H, D) qkv projection
+    for name, off in (("q", 0), ("k", 4 * 72 * 2), ("v", 2 * 4 * 72 * 2)):
+        setattr(a, name, _lib.Tensor4(0x10000 + off, 256 * 3 * 4 * 72, 3 * 4 * 72, 72))
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 1) == 0
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 0) == 0
+
+
+@pytest.mark.parametrize("field,value,status", [
+    ("dtype", 7, 2),
+    ("head_dim", 48, 3), ("head_dim", 76, 3), ("head_dim", 136, 3),
+    ("seqlen_q", 100, 4), ("seqlen_kv", 0, 4), ("seqlen_kv", 130, 4),
+    ("batch", 0, 5), ("heads", 0, 5),
+])
+def test_validation_rejects_bad_sizes(field, value, status):
+    lib = _lib.load()
+    a = _good_args()
+    setattr(a, field, value)
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 1) == status
+
+
+def test_validation_rejects_bad_pointers_and_strides():
+    lib = _lib.load()
+    a = _good_args()
+    a.q = _lib.Tensor4(0, 1, 1, 1)
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 1) == 1          # NULL
+    a = _good_args()
+    a.k = _lib.Tensor4(0x10008, 256 * 4 * 72, 4 * 72, 72)
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 1) == 7          # misaligned base
+    a = _good_args()
+    a.v = _lib.Tensor4(0x10000, 256 * 4 * 72, 4 * 72 + 4, 72)
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 1) == 6          # stride not a multiple of 16 bytes
+    a = _good_args()
+    a.tq = _lib.Tensor4(0, 1, 1, 1)
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 1) == 1          # tangents required by the dual pass
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 0) == 0          # ... and ignored by the plain one
+    a = _good_args()
+    a.lse = None
+    assert lib.dmf_attn_validate_fwd(C.byref(a), 0) == 1
+    assert lib.dmf_attn_validate_fwd(None, 0) == 1
+
+
+def test_compute_entry_points_fail_loudly_without_a_gpu():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    lib = _lib.load()
+    a = _good_args()
+    # no device: a status, not a crash and not a silent CPU computation
+    assert lib.dmf_attn_fwd_dual(C.byref(a)) == 8
+    assert lib.dmf_attn_fwd(C.byref(a)) == 8
+    from dmf_b200 import flash_attn_func
+    q = torch.randn(1, 128, 1, 64)
+    with pytest.raises(Exception):
+        flash_attn_func(q, q, q)
