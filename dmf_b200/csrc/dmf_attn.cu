@@ -10,6 +10,7 @@
 #include <cmath>
 #include <cstring>
 
+#include "attn_bwd.cuh"
 #include "attn_fwd.cuh"
 
 namespace {
@@ -229,7 +230,8 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
 
 size_t bwd_workspace_bytes(int batch, int lq, int lkv, int heads, int d) {
   if (check_dims(batch, lq, lkv, heads, d, DMF_ATTN_BF16) != DMF_ATTN_OK) return 0;
-  return 0;
+  // -lse*log2(e) and delta = rowsum(dO*O), one float per query row each
+  return 2 * sizeof(float) * static_cast<size_t>(batch) * heads * lq;
 }
 
 int validate_bwd(const dmf_attn_bwd_args* a) {
@@ -242,14 +244,81 @@ int validate_bwd(const dmf_attn_bwd_args* a) {
   for (const dmf_attn_tensor* t : ts)
     if ((st = check_tensor(*t, 2)) != DMF_ATTN_OK) return st;
   const size_t need = bwd_workspace_bytes(a->batch, a->seqlen_q, a->seqlen_kv, a->heads, a->head_dim);
-  if (need > 0 && (a->workspace == nullptr || a->workspace_bytes < need)) return DMF_ATTN_ERR_WORKSPACE;
+  if (a->workspace == nullptr || a->workspace_bytes < need) return DMF_ATTN_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(a->workspace) & 15u) != 0) return DMF_ATTN_ERR_ALIGN;
   return DMF_ATTN_OK;
+}
+
+template <typename T, int TAIL, int kMode>
+int launch_bwd_inst(const BwdParams& p, int grid, cudaStream_t stream) {
+  using TR = BwdTraits<TAIL>;
+  auto kernel = attn_bwd_kernel<T, TAIL, kMode>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::kSmemBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_LAUNCH;
+  }
+  kernel<<<grid, kFwdThreads, TR::kSmemBytes, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
+}
+
+template <typename T, int kMode>
+int launch_bwd_tail(const BwdParams& p, int tail, int grid, cudaStream_t stream) {
+  switch (tail) {
+    case 0: return launch_bwd_inst<T, 0, kMode>(p, grid, stream);
+    case 16: return launch_bwd_inst<T, 16, kMode>(p, grid, stream);
+    case 32: return launch_bwd_inst<T, 32, kMode>(p, grid, stream);
+    case 64: return launch_bwd_inst<T, 64, kMode>(p, grid, stream);
+    default: return DMF_ATTN_ERR_HEAD_DIM;
+  }
 }
 
 int run_bwd(const dmf_attn_bwd_args* a) {
   int st = validate_bwd(a);
   if (st != DMF_ATTN_OK) return st;
-  return DMF_ATTN_ERR_LAUNCH;
+  int sm_count = 0;
+  if ((st = device_info(&sm_count)) != DMF_ATTN_OK) return st;
+  const int tail = tail_of(a->head_dim);
+  const int B = a->batch, H = a->heads, D = a->head_dim, Lq = a->seqlen_q, Lk = a->seqlen_kv, dt = a->dtype;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+
+  BwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.o = a->o.ptr; p.o_sb = a->o.stride_b; p.o_sl = a->o.stride_l; p.o_sh = a->o.stride_h;
+  p.dout = a->dout.ptr; p.do_sb = a->dout.stride_b; p.do_sl = a->dout.stride_l; p.do_sh = a->dout.stride_h;
+  p.lse = a->lse;
+  p.ws_neg_lse2 = static_cast<float*>(a->workspace);
+  p.ws_delta = p.ws_neg_lse2 + static_cast<size_t>(B) * H * Lq;
+  p.status_word = a->status_word;
+  p.batch = B; p.heads = H; p.seqlen_q = Lq; p.seqlen_kv = Lk; p.head_dim = D;
+  p.scale = a->softmax_scale;
+  p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
+
+  // pass 1: dQ (query tiles resident, K/V streamed); also fills the workspace
+  if ((st = make_map_pair(&p.r0_main, &p.r0_tail, a->q, dt, B, Lq, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.r1_main, &p.r1_tail, a->dout, dt, B, Lq, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.x0_main, &p.x0_tail, a->k, dt, B, Lk, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.x1_main, &p.x1_tail, a->v, dt, B, Lk, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  p.out0 = a->dq.ptr; p.out0_sb = a->dq.stride_b; p.out0_sl = a->dq.stride_l; p.out0_sh = a->dq.stride_h;
+  p.tiles_per_bh = Lq / 128;
+  p.num_tiles = B * H * p.tiles_per_bh;
+  p.inner_blocks = Lk / 128;
+  int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
+  st = dt == DMF_ATTN_BF16 ? launch_bwd_tail<__nv_bfloat16, kModeDQ>(p, tail, grid, stream)
+                           : launch_bwd_tail<__half, kModeDQ>(p, tail, grid, stream);
+  if (st != DMF_ATTN_OK) return st;
+
+  // pass 2: dK, dV (key tiles resident, Q/dO and the workspace rows streamed)
+  BwdParams p2 = p;
+  p2.r0_main = p.x0_main; p2.r0_tail = p.x0_tail; p2.r1_main = p.x1_main; p2.r1_tail = p.x1_tail;
+  p2.x0_main = p.r0_main; p2.x0_tail = p.r0_tail; p2.x1_main = p.r1_main; p2.x1_tail = p.r1_tail;
+  p2.out0 = a->dk.ptr; p2.out0_sb = a->dk.stride_b; p2.out0_sl = a->dk.stride_l; p2.out0_sh = a->dk.stride_h;
+  p2.out1 = a->dv.ptr; p2.out1_sb = a->dv.stride_b; p2.out1_sl = a->dv.stride_l; p2.out1_sh = a->dv.stride_h;
+  p2.tiles_per_bh = Lk / 128;
+  p2.num_tiles = B * H * p2.tiles_per_bh;
+  p2.inner_blocks = Lq / 128;
+  grid = p2.num_tiles < sm_count ? p2.num_tiles : sm_count;
+  return dt == DMF_ATTN_BF16 ? launch_bwd_tail<__nv_bfloat16, kModeDKV>(p2, tail, grid, stream)
+                             : launch_bwd_tail<__half, kModeDKV>(p2, tail, grid, stream);
 }
 
 }  // namespace
