@@ -18,13 +18,13 @@ BF16, FP16 = 0, 1
 STATUS_NAMES = {
     0: "OK", 1: "ERR_NULL", 2: "ERR_DTYPE", 3: "ERR_HEAD_DIM", 4: "ERR_SEQLEN", 5: "ERR_SHAPE",
     6: "ERR_STRIDE", 7: "ERR_ALIGN", 8: "ERR_DEVICE", 9: "ERR_TENSOR_MAP", 10: "ERR_LAUNCH",
-    11: "ERR_WORKSPACE", 12: "ERR_TIMEOUT",
+    11: "ERR_WORKSPACE", 12: "ERR_TIMEOUT", 13: "ERR_TOO_LARGE",
 }
 
 # every symbol include/dmf_attn.h declares
 EXPORTS = (
     "dmf_attn_abi_version", "dmf_attn_status_string", "dmf_attn_fwd_dual", "dmf_attn_fwd",
-    "dmf_attn_bwd", "dmf_attn_bwd_workspace_bytes", "dmf_attn_check_status_word",
+    "dmf_attn_bwd", "dmf_attn_bwd_static", "dmf_attn_bwd_workspace_bytes", "dmf_attn_check_status_word",
     "dmf_attn_validate_fwd", "dmf_attn_validate_bwd",
 )
 
@@ -88,8 +88,10 @@ def load() -> C.CDLL:
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(FwdArgs)]
-        lib.dmf_attn_bwd.restype = C.c_int
-        lib.dmf_attn_bwd.argtypes = [C.POINTER(BwdArgs)]
+        for name in ("dmf_attn_bwd", "dmf_attn_bwd_static"):
+            fn = getattr(lib, name)
+            fn.restype = C.c_int
+            fn.argtypes = [C.POINTER(BwdArgs)]
         lib.dmf_attn_bwd_workspace_bytes.restype = C.c_size_t
         lib.dmf_attn_bwd_workspace_bytes.argtypes = [C.c_int32] * 5
         lib.dmf_attn_check_status_word.restype = C.c_int

@@ -321,6 +321,57 @@ int run_bwd(const dmf_attn_bwd_args* a) {
                              : launch_bwd_tail<__half, kModeDKV>(p2, tail, grid, stream);
 }
 
+// ---- backward without a caller-provided workspace ----
+
+// Scratch of dmf_attn_bwd_static: -lse*log2(e) and delta for up to DMF_ATTN_STATIC_MAX_ROWS query
+// rows.  In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_bwd_static_scratch[2 * DMF_ATTN_STATIC_MAX_ROWS];
+
+struct StaticScratch {
+  std::atomic<int> ready{0};
+  float* ptr = nullptr;
+};
+StaticScratch g_static_scratch[kMaxDevices];
+
+// Device address of the scratch array on the current device (looked up once per device).
+int static_scratch_ptr(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_DEVICE;
+  }
+  StaticScratch& s = g_static_scratch[dev];
+  if (s.ready.load(std::memory_order_acquire) == 0) {
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_bwd_static_scratch) != cudaSuccess || addr == nullptr) {
+      (void)cudaGetLastError();
+      return DMF_ATTN_ERR_DEVICE;
+    }
+    s.ptr = static_cast<float*>(addr);  // every racing first caller computes the same value
+    s.ready.store(1, std::memory_order_release);
+  }
+  *out = s.ptr;
+  return DMF_ATTN_OK;
+}
+
+int run_bwd_static(const dmf_attn_bwd_args* a) {
+  if (a == nullptr) return DMF_ATTN_ERR_NULL;
+  int st = check_dims(a->batch, a->seqlen_q, a->seqlen_kv, a->heads, a->head_dim, a->dtype);
+  if (st != DMF_ATTN_OK) return st;
+  const int64_t rows = static_cast<int64_t>(a->batch) * a->heads * a->seqlen_q;
+  if (rows > DMF_ATTN_STATIC_MAX_ROWS) return DMF_ATTN_ERR_TOO_LARGE;
+  dmf_attn_bwd_args local = *a;
+  local.workspace = reinterpret_cast<void*>(static_cast<uintptr_t>(256));  // placeholder for validation only
+  local.workspace_bytes = sizeof(g_bwd_static_scratch);
+  if ((st = validate_bwd(&local)) != DMF_ATTN_OK) return st;
+  int sm_count = 0;
+  if ((st = device_info(&sm_count)) != DMF_ATTN_OK) return st;
+  float* scratch = nullptr;
+  if ((st = static_scratch_ptr(&scratch)) != DMF_ATTN_OK) return st;
+  local.workspace = scratch;
+  return run_bwd(&local);
+}
+
 }  // namespace
 
 #define DMF_API __attribute__((visibility("default")))
@@ -344,6 +395,7 @@ DMF_API const char* dmf_attn_status_string(int status) {
     case DMF_ATTN_ERR_LAUNCH: return "kernel launch failed";
     case DMF_ATTN_ERR_WORKSPACE: return "workspace missing or too small";
     case DMF_ATTN_ERR_TIMEOUT: return "a device-side wait ran out";
+    case DMF_ATTN_ERR_TOO_LARGE: return "batch*heads*seqlen_q exceeds the built-in scratch of dmf_attn_bwd_static (1048576 rows)";
     default: return "unknown status";
   }
 }
@@ -362,6 +414,8 @@ DMF_API size_t dmf_attn_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int
 }
 
 DMF_API int dmf_attn_bwd(const dmf_attn_bwd_args* args) { return run_bwd(args); }
+
+DMF_API int dmf_attn_bwd_static(const dmf_attn_bwd_args* args) { return run_bwd_static(args); }
 
 DMF_API int dmf_attn_check_status_word(const int32_t* status_word, void* stream, int32_t* raw) {
   if (status_word == nullptr) return DMF_ATTN_ERR_NULL;

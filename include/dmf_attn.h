@@ -44,7 +44,8 @@ enum dmf_attn_status {
   DMF_ATTN_ERR_TENSOR_MAP = 9,  /* the driver rejected a TMA tensor map                        */
   DMF_ATTN_ERR_LAUNCH = 10,     /* the kernel launch failed (see cudaGetLastError)             */
   DMF_ATTN_ERR_WORKSPACE = 11,  /* workspace missing or too small                              */
-  DMF_ATTN_ERR_TIMEOUT = 12     /* a device-side wait ran out (reported by dmf_attn_check_status_word) */
+  DMF_ATTN_ERR_TIMEOUT = 12,    /* a device-side wait ran out (reported by dmf_attn_check_status_word) */
+  DMF_ATTN_ERR_TOO_LARGE = 13   /* problem exceeds the built-in scratch of dmf_attn_bwd_static         */
 };
 
 /* One (B, L, H, D) tensor: base pointer and element strides; the D stride is 1. */
@@ -143,6 +144,37 @@ int dmf_attn_bwd(const dmf_attn_bwd_args* args);
 /* Bytes of workspace dmf_attn_bwd needs for this problem size (0 on bad sizes). */
 size_t dmf_attn_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t seqlen_kv,
                                     int32_t heads, int32_t head_dim);
+
+/*
+ * Primal backward for callers that have no way to hand over scratch memory.
+ * (No counterpart in the reference: its backward lets the FlashAttention
+ * library allocate whatever it needs through torch.)
+ *
+ * Some hosts of this library cannot allocate device memory at the point where
+ * they need a backward pass: a plugin that is given input and output buffers by
+ * a framework whose allocator it cannot reach, a service running inside a fixed
+ * memory reservation, a step that must not call cudaMalloc because that call
+ * synchronises the whole device.  For them this entry point does exactly what
+ * dmf_attn_bwd does, but takes its scratch (two floats per query row) from a
+ * fixed array that lives inside the library image instead of args->workspace,
+ * which is ignored together with args->workspace_bytes.  It calls no
+ * cudaMalloc, cudaFree or any other allocating routine.
+ *
+ * Limit: batch * heads * seqlen_q <= DMF_ATTN_STATIC_MAX_ROWS (1,048,576 rows,
+ * i.e. 8 MiB of device memory, held by every GPU that loads the library until
+ * the process exits).  Larger problems return DMF_ATTN_ERR_TOO_LARGE and launch
+ * nothing.
+ *
+ * The first call on each device looks the array's device address up (with that
+ * device current) and caches it; make that first call outside any stream
+ * capture.  All calls on a device share the one array: its contents are
+ * overwritten by every call (nothing in it needs clearing - the first pass
+ * writes every slot the second pass reads), so two calls whose kernels may
+ * overlap on the GPU (different streams, no dependency) race with each other
+ * and must be ordered by the caller.
+ */
+#define DMF_ATTN_STATIC_MAX_ROWS (1 << 20)
+int dmf_attn_bwd_static(const dmf_attn_bwd_args* args);
 
 /*
  * Copy a status word back (synchronises the stream) and translate it:

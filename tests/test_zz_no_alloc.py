@@ -1,0 +1,83 @@
+"""dmf_attn_bwd_static: the backward for hosts that cannot provide scratch memory.
+
+A plugin that only receives input and output buffers, or a process pinned inside a
+fixed memory reservation, has no allocator to ask for the backward's workspace and
+may not call cudaMalloc itself.  The library therefore carries its own fixed scratch
+array and offers this entry point, which takes no workspace.  The test calls it
+through the C ABI twice in a row, on different data, and checks each result against
+the regular entry point (dmf_attn_bwd, caller-provided workspace): both run the same
+kernels in the same order, so the results must agree bit for bit, and the second
+call must not be disturbed by what the first one left behind in the shared array.
+
+This file sorts last on purpose: a run that stops at the first failure has then
+already exercised every other test.
+"""
+
+import ctypes as C
+
+import pytest
+import torch
+
+from dmf_b200 import _lib
+from oracle import attn_jvp_oracle as orc
+from tests import _cabi
+
+DEV = "cuda:0"
+
+
+def _bwd_static(dout, q, k, v, o, lse, expect=0):
+    """Call dmf_attn_bwd_static with NaN-filled outputs and NO workspace."""
+    dq, dk, dv = (torch.full(x.shape, float("nan"), dtype=x.dtype, device=x.device) for x in (q, k, v))
+    sw = torch.zeros(1, dtype=torch.int32, device=q.device)
+    a = _lib.BwdArgs()
+    B, Lq, H, D = q.shape
+    a.batch, a.seqlen_q, a.seqlen_kv, a.heads, a.head_dim = B, Lq, k.shape[1], H, D
+    a.dtype = _lib.BF16 if q.dtype == torch.bfloat16 else _lib.FP16
+    a.softmax_scale = float(D ** -0.5)
+    a.dout, a.q, a.k, a.v, a.o = (_cabi.t4(x) for x in (dout, q, k, v, o))
+    a.dq, a.dk, a.dv = (_cabi.t4(x) for x in (dq, dk, dv))
+    a.lse = lse.data_ptr()
+    a.workspace, a.workspace_bytes = None, 0          # ignored by this entry point
+    a.status_word = sw.data_ptr()
+    a.stream = torch.cuda.current_stream(q.device).cuda_stream
+    lib = _lib.load()
+    st = lib.dmf_attn_bwd_static(C.byref(a))
+    assert st == expect, f"status {st}: {lib.dmf_attn_status_string(st).decode()}"
+    if st == 0:
+        raw = C.c_int32(0)
+        assert lib.dmf_attn_check_status_word(sw.data_ptr(), a.stream, C.byref(raw)) == 0, raw.value
+    return dq, dk, dv
+
+
+@pytest.mark.gpu
+def test_static_scratch_backward_matches_regular_backward_twice():
+    shapes = [(3, 256, 4, 72, 21), (2, 512, 2, 64, 22)]   # two calls in a row, different sizes and data
+    for B, L, H, D, seed in shapes:
+        q, k, v, _, _, _, dout = (x.bfloat16().to(DEV) for x in orc.make_inputs(B, L, H, D, seed=seed, n_extra=1))
+        o, _, lse, _ = _cabi.fwd(q, k, v)
+        ref_dq, ref_dk, ref_dv, _ = _cabi.bwd(dout, q, k, v, o, lse)        # existing entry point
+        dq, dk, dv = _bwd_static(dout, q, k, v, o, lse)                      # new entry point
+        for got, want in ((dq, ref_dq), (dk, ref_dk), (dv, ref_dv)):
+            assert not torch.isnan(got).any()
+            assert torch.equal(got, want)
+        # and both are right, not merely equal
+        gq, gk, gv = orc.attn_bwd_closed_form(*[x.float().cpu() for x in (q, k, v, dout)])
+        for got, want in ((dq, gq), (dk, gk), (dv, gv)):
+            assert orc.rel_l2(got.float().cpu(), want) < 8e-3
+
+
+@pytest.mark.gpu
+def test_static_scratch_backward_rejects_oversized_problem():
+    # batch * heads * seqlen_q = 2^20 + 128 rows > the built-in scratch: refused before any launch.
+    # Validation happens before the tensors are touched, so tiny stand-in buffers are enough.
+    x = torch.zeros(1, 128, 1, 64, device=DEV, dtype=torch.bfloat16)
+    lse = torch.zeros(1, 1, 128, device=DEV)
+    a = _lib.BwdArgs()
+    a.batch, a.seqlen_q, a.seqlen_kv, a.heads, a.head_dim = 8193, 128, 128, 1, 64
+    a.dtype, a.softmax_scale = _lib.BF16, 0.125
+    for n in ("dout", "q", "k", "v", "o", "dq", "dk", "dv"):
+        setattr(a, n, _cabi.t4(x))
+    a.lse = lse.data_ptr()
+    lib = _lib.load()
+    assert lib.dmf_attn_bwd_static(C.byref(a)) == 13
+    assert b"1048576" in lib.dmf_attn_status_string(13)
