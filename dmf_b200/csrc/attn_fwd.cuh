@@ -49,8 +49,10 @@ constexpr int kRoleProducer = 100, kRoleMma = 200, kRoleSoftmax = 300;
 
 struct FwdParams {
   // TMA maps of (D, L, H, B) views; "main" = columns [0,64), "tail" = [64, 64+TAIL)
-  CUtensorMap q_main, q_tail, k_main, k_tail, v_main, v_tail;
-  CUtensorMap tq_main, tq_tail, tk_main, tk_tail, tv_main, tv_tail;
+  CUtensorMap q_main, q_tail, k_main, k_tail;
+  CUtensorMap tq_main, tq_tail, tk_main, tk_tail;
+  // V and dV: boxes of 32 columns x 128 rows with 64-byte swizzle ("atoms"), see FwdTraits
+  CUtensorMap v_map, tv_map;
   void* o;
   void* to;
   float* lse;
@@ -74,7 +76,15 @@ struct FwdTraits {
   static constexpr int kStagesV = (kDual && TAIL == 32) ? 1 : 2;
   static constexpr int kStagesK_ = (kDual && TAIL == 64) ? 1 : kStagesK;
   static constexpr int kStagesV_ = (kDual && TAIL == 64) ? 1 : kStagesV;
-  static constexpr int kTileSmem = kGroupBytes * (1 + kStagesK_ + kStagesV_);
+  // V / dV blocks are the MN-major operand of the P V products.  They are stored as
+  // ceil(DPAD/32) atoms of 32 columns x 128 rows (64-byte swizzle) so that one MMA of N = DPAD
+  // covers the whole head dim; a split into a 64- and a 16-column MMA costs far more than the
+  // 16 extra columns (a tcgen05.mma of N = 16 takes about as long as one of N = 128).
+  static constexpr int kVAtoms = (kDPad + 31) / 32;
+  static constexpr int kVAtomBytes = 128 * 64;
+  static constexpr int kVTileBytes = kVAtoms * kVAtomBytes;
+  static constexpr int kVGroupBytes = kGroup * kVTileBytes;
+  static constexpr int kTileSmem = kGroupBytes * (1 + kStagesK_) + kVGroupBytes * kStagesV_;
   // barriers
   static constexpr int kBarQFull = 0, kBarQEmpty = 1, kBarSFull = 2, kBarDSFull = 3, kBarPFull = 4,
                        kBarGFull = 5, kBarAccFull = 6 /* and 7 */, kBarKFull = 8,
@@ -129,6 +139,18 @@ __device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t a_tmem, uint3
   }
 }
 
+// Same product with V stored as 64-byte-swizzled atoms of 32 columns: one MMA of N = DPAD per K-step.
+template <typename TR>
+__device__ __forceinline__ void issue_pv_atoms(uint32_t d_tmem, uint32_t a_tmem, uint32_t v_tile,
+                                               uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < kBlockKV / 16; ++kk) {
+    // leading-dim offset = next 32-column atom, stride offset = next group of 8 kv rows
+    const uint64_t bd = make_smem_desc(v_tile + kk * (16 * 64), TR::kVAtomBytes, 8 * 64, kSwizzle64);
+    mma_ts(d_tmem, a_tmem + kk * 8, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
 // ---- the kernel ---------------------------------------------------------------
 
 template <typename T, int TAIL, bool kDual>
@@ -177,7 +199,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     if (lane == 0) {
       prefetch_tensor_map(&p.q_main);
       prefetch_tensor_map(&p.k_main);
-      prefetch_tensor_map(&p.v_main);
+      prefetch_tensor_map(&p.v_map);
       uint32_t kcnt = 0, vcnt = 0, tcnt = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcnt) {
@@ -218,14 +240,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             ok = mbar_wait(bar(TR::kBarVEmpty + s), ph ^ 1u, abort_flag, p.status_word,
                            kRoleProducer + TR::kBarVEmpty);
             if (!ok) break;
-            const uint32_t dst = s_v + s * TR::kGroupBytes, fb = bar(TR::kBarVFull + s);
-            mbar_arrive_expect_tx(fb, TR::kGroupBytes);
-            tma_load_4d(dst, &p.v_main, fb, 0, kv0, h, b);
-            if constexpr (TAIL > 0) tma_load_4d(dst + TR::kMainBytes, &p.v_tail, fb, 64, kv0, h, b);
-            if constexpr (kDual) {
-              tma_load_4d(dst + TR::kTileBytes, &p.tv_main, fb, 0, kv0, h, b);
-              if constexpr (TAIL > 0)
-                tma_load_4d(dst + TR::kTileBytes + TR::kMainBytes, &p.tv_tail, fb, 64, kv0, h, b);
+            const uint32_t dst = s_v + s * TR::kVGroupBytes, fb = bar(TR::kBarVFull + s);
+            mbar_arrive_expect_tx(fb, TR::kVGroupBytes);
+#pragma unroll
+            for (int a = 0; a < TR::kVAtoms; ++a) {
+              tma_load_4d(dst + a * TR::kVAtomBytes, &p.v_map, fb, a * 32, kv0, h, b);
+              if constexpr (kDual)
+                tma_load_4d(dst + TR::kVTileBytes + a * TR::kVAtomBytes, &p.tv_map, fb, a * 32, kv0, h, b);
             }
             ++vcnt;
           }
@@ -236,8 +257,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     // ============================ MMA issuer ================================
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(kBf16, false, false, 128, 128);
-      constexpr uint32_t idesc_pv_main = make_idesc(kBf16, false, true, 128, 64);
-      constexpr uint32_t idesc_pv_tail = make_idesc(kBf16, false, true, 128, TAIL > 0 ? TAIL : 16);
+      constexpr uint32_t idesc_pv = make_idesc(kBf16, false, true, 128, DPAD);
       const uint32_t t_s = tmem + TR::kColS, t_ds = tmem + TR::kColDS;
       const uint32_t t_o = tmem + TR::kColO, t_t = tmem + TR::kColT;
       uint32_t kcnt = 0, vcnt = 0, tcnt = 0, pcnt = 0, gcnt = 0, scnt = 0;
@@ -266,15 +286,15 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           if (num_kv_blocks == 1) tc_commit(bar(TR::kBarQEmpty));
           for (int j = 0; j < num_kv_blocks; ++j) {
             const uint32_t sv = vcnt % TR::kStagesV_;
-            const uint32_t vt = s_v + sv * TR::kGroupBytes;
+            const uint32_t vt = s_v + sv * TR::kVGroupBytes;
             ok = wait(TR::kBarVFull + sv, (vcnt / TR::kStagesV_) & 1u);
             if (!ok) break;
             ok = wait(TR::kBarPFull, pcnt & 1u);
             if (!ok) break;
             ++pcnt;
             tc_fence_after_sync();
-            issue_pv<TAIL, TR>(t_o, t_s, vt, idesc_pv_main, idesc_pv_tail, j > 0);                  // O += P V
-            issue_pv<TAIL, TR>(t_t, t_s, vt + TR::kTileBytes, idesc_pv_main, idesc_pv_tail, j > 0); // T += P dV
+            issue_pv_atoms<TR>(t_o, t_s, vt, idesc_pv, j > 0);                    // O += P V
+            issue_pv_atoms<TR>(t_t, t_s, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
             const bool more = (j + 1 < num_kv_blocks);
             if (more) {
               sk = kcnt % TR::kStagesK_;
@@ -289,7 +309,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             if (!ok) break;
             ++gcnt;
             tc_fence_after_sync();
-            issue_pv<TAIL, TR>(t_t, t_ds, vt, idesc_pv_main, idesc_pv_tail, true);  // T += G V
+            issue_pv_atoms<TR>(t_t, t_ds, vt, idesc_pv, true);  // T += G V
             tc_commit(bar(TR::kBarAccFull));
             tc_commit(bar(TR::kBarVEmpty + sv));
             ++vcnt;
@@ -333,8 +353,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             ok = wait(TR::kBarPFull + (pcnt & 1u), (pcnt >> 1) & 1u);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_pv<TAIL, TR>(t_o, (pcnt & 1u) ? t_ds : t_s, s_v + sv * TR::kGroupBytes, idesc_pv_main,
-                               idesc_pv_tail, j > 0);
+            issue_pv_atoms<TR>(t_o, (pcnt & 1u) ? t_ds : t_s, s_v + sv * TR::kVGroupBytes, idesc_pv, j > 0);
             tc_commit(bar(TR::kBarAccFull + (pcnt & 1u)));
             ++pcnt;
             tc_commit(bar(TR::kBarVEmpty + sv));

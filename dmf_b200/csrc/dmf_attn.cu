@@ -198,11 +198,11 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
   const int B = a->batch, H = a->heads, D = a->head_dim, Lq = a->seqlen_q, Lk = a->seqlen_kv, dt = a->dtype;
   if ((st = make_map_pair(&p.q_main, &p.q_tail, a->q, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
   if ((st = make_map_pair(&p.k_main, &p.k_tail, a->k, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
-  if ((st = make_map_pair(&p.v_main, &p.v_tail, a->v, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
+  if ((st = make_map(&p.v_map, a->v, dt, B, Lk, H, D, 32, kBlockKV, CU_TENSOR_MAP_SWIZZLE_64B)) != DMF_ATTN_OK) return st;
   if (dual) {
     if ((st = make_map_pair(&p.tq_main, &p.tq_tail, a->tq, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
     if ((st = make_map_pair(&p.tk_main, &p.tk_tail, a->tk, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
-    if ((st = make_map_pair(&p.tv_main, &p.tv_tail, a->tv, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
+    if ((st = make_map(&p.tv_map, a->tv, dt, B, Lk, H, D, 32, kBlockKV, CU_TENSOR_MAP_SWIZZLE_64B)) != DMF_ATTN_OK) return st;
   }
   p.o = a->o.ptr;
   p.o_sb = a->o.stride_b; p.o_sl = a->o.stride_l; p.o_sh = a->o.stride_h;
