@@ -405,11 +405,11 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(r[c][i]));
-            mx1 = fmaxf(mx1, __uint_as_float(r[c][i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(r[c][i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(r[c][i + 3]));
+          for (int i = 0; i < 32; i += 8) {
+            mx0 = max3(mx0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+            mx1 = max3(mx1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+            mx2 = max3(mx2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+            mx3 = max3(mx3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
           }
         }
         const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
@@ -439,24 +439,30 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             tmem_wait_st();
           }
         }
-        const float neg_m = -m_used;
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        // P = exp2(S * c - m), two elements per fp32 instruction
+        const uint64_t sl2_2 = pack_f2(sl2, sl2), neg_m2 = pack_f2(-m_used, -m_used);
+        uint64_t la = pack_f2(0.f, 0.f), lb = la;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(r[c][i]), sl2, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(r[c][i + 1]), sl2, neg_m));
-            const float p2 = fast_exp2(fmaf(__uint_as_float(r[c][i + 2]), sl2, neg_m));
-            const float p3 = fast_exp2(fmaf(__uint_as_float(r[c][i + 3]), sl2, neg_m));
-            l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+            float x0, x1, x2, x3;
+            unpack_f2(fma2(pack_u2(r[c][i], r[c][i + 1]), sl2_2, neg_m2), x0, x1);
+            unpack_f2(fma2(pack_u2(r[c][i + 2], r[c][i + 3]), sl2_2, neg_m2), x2, x3);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+            la = add2(la, pack_f2(p0, p1));
+            lb = add2(lb, pack_f2(p2, p3));
             r[c][i] = __float_as_uint(p0);
             r[c][i + 1] = __float_as_uint(p1);
             r[c][i + 2] = __float_as_uint(p2);
             r[c][i + 3] = __float_as_uint(p3);
           }
         }
-        l += (l0 + l1) + (l2 + l3);
+        {
+          float s0, s1;
+          unpack_f2(add2(la, lb), s0, s1);
+          l += s0 + s1;
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
@@ -474,7 +480,8 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           ok = wait(TR::kBarDSFull, gblk & 1u);
           if (!ok) break;
           tc_fence_after_sync();
-          float mu0 = 0.f, mu1 = 0.f;
+          const uint64_t scale2 = pack_f2(p.scale, p.scale);
+          uint64_t mua = pack_f2(0.f, 0.f), mub = mua;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t d[32];
@@ -482,16 +489,25 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             tmem_wait_ld();
             uint32_t pk[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float g0 = __uint_as_float(r[c][2 * i]) * (__uint_as_float(d[2 * i]) * p.scale);
-              const float g1 = __uint_as_float(r[c][2 * i + 1]) * (__uint_as_float(d[2 * i + 1]) * p.scale);
-              mu0 += g0;
-              mu1 += g1;
+            for (int i = 0; i < 16; i += 2) {
+              const uint64_t ga = mul2(pack_u2(r[c][2 * i], r[c][2 * i + 1]), mul2(pack_u2(d[2 * i], d[2 * i + 1]), scale2));
+              const uint64_t gb = mul2(pack_u2(r[c][2 * i + 2], r[c][2 * i + 3]),
+                                       mul2(pack_u2(d[2 * i + 2], d[2 * i + 3]), scale2));
+              mua = add2(mua, ga);
+              mub = add2(mub, gb);
+              float g0, g1, g2, g3;
+              unpack_f2(ga, g0, g1);
+              unpack_f2(gb, g2, g3);
               pk[i] = Pack2<T>::pack(g0, g1);
+              pk[i + 1] = Pack2<T>::pack(g2, g3);
             }
             tmem_st_x16(t_ds + c * 16, pk);
           }
-          mu += mu0 + mu1;
+          {
+            float s0, s1;
+            unpack_f2(add2(mua, mub), s0, s1);
+            mu += s0 + s1;
+          }
           tmem_wait_st();
           tc_fence_before_sync();
           mbar_arrive(bar(TR::kBarGFull));
