@@ -27,6 +27,7 @@
 namespace dmf {
 
 constexpr int kModeDQ = 0, kModeDKV = 1;
+constexpr int kBwdThreads = 192;  // TMA warp, MMA warp, one softmax warpgroup
 
 struct BwdParams {
   // resident / streamed operand maps, "main" = columns [0,64), "tail" = [64, 64+TAIL)
@@ -91,7 +92,7 @@ __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
 }
 
 template <typename T, int TAIL, int kMode>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ BwdParams p) {
   using TR = BwdTraits<TAIL>;
   constexpr int DPAD = TR::kDPad;
@@ -176,7 +177,9 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     }
   } else if (warp == 1) {
     // ============================ MMA issuer ================================
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
+      auto commit = [&](int b_) { if (leader) tc_commit(bar(b_)); };
       constexpr uint32_t idesc_qk = make_idesc(kBf16, false, false, 128, 128);
       constexpr uint32_t idesc_pv_main = make_idesc(kBf16, false, true, 128, 64);
       constexpr uint32_t idesc_pv_tail = make_idesc(kBf16, false, true, 128, TAIL > 0 ? TAIL : 16);
@@ -185,7 +188,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       uint32_t xcnt = 0, tcnt = 0, pcnt = 0, gcnt = 0;
       bool ok = true;
       auto wait = [&](int b_, uint32_t parity) -> bool {
-        return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_);
+        return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_));
       };
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcnt) {
         ok = wait(TR::kBarRFull, tcnt & 1u);
@@ -195,11 +198,11 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         if (!ok) break;
         tc_fence_after_sync();
         uint32_t xt = s_x + s * TR::kGroupBytes;
-        issue_qk<TAIL, TR>(t_s, s_r, xt, idesc_qk, false);                                    // S  = R0 X0^T
-        tc_commit(bar(TR::kBarSFull));
-        issue_qk<TAIL, TR>(t_d, s_r + TR::kTileBytes, xt + TR::kTileBytes, idesc_qk, false);  // dP = R1 X1^T
-        tc_commit(bar(TR::kBarDFull));
-        if (J == 1) tc_commit(bar(TR::kBarREmpty));
+        issue_qk<TAIL, TR>(leader, t_s, s_r, xt, idesc_qk, false);                                    // S  = R0 X0^T
+        commit(TR::kBarSFull);
+        issue_qk<TAIL, TR>(leader, t_d, s_r + TR::kTileBytes, xt + TR::kTileBytes, idesc_qk, false);  // dP = R1 X1^T
+        commit(TR::kBarDFull);
+        if (J == 1) commit(TR::kBarREmpty);
         for (int j = 0; j < J; ++j) {
           const uint32_t s_cur = s, xt_cur = xt;
           ok = wait(TR::kBarPFull, pcnt & 1u);
@@ -207,7 +210,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
           ++pcnt;
           tc_fence_after_sync();
           if constexpr (kDKV)  // dV += P^T dO
-            issue_pv<TAIL, TR>(t_a1, t_s, xt_cur + TR::kTileBytes, idesc_pv_main, idesc_pv_tail, j > 0);
+            issue_pv<TAIL, TR>(leader, t_a1, t_s, xt_cur + TR::kTileBytes, idesc_pv_main, idesc_pv_tail, j > 0);
           const bool more = (j + 1 < J);
           if (more) {
             s = (xcnt + 1) % TR::kStages;
@@ -215,21 +218,21 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
             if (!ok) break;
             tc_fence_after_sync();
             xt = s_x + s * TR::kGroupBytes;
-            issue_qk<TAIL, TR>(t_s, s_r, xt, idesc_qk, false);
-            tc_commit(bar(TR::kBarSFull));
+            issue_qk<TAIL, TR>(leader, t_s, s_r, xt, idesc_qk, false);
+            commit(TR::kBarSFull);
           }
           ok = wait(TR::kBarGFull, gcnt & 1u);
           if (!ok) break;
           ++gcnt;
           tc_fence_after_sync();
-          issue_pv<TAIL, TR>(t_a0, t_d, xt_cur, idesc_pv_main, idesc_pv_tail, j > 0);  // dQ += dS K   /   dK += dS^T Q
-          tc_commit(bar(TR::kBarAccFull));
-          tc_commit(bar(TR::kBarXEmpty + s_cur));
+          issue_pv<TAIL, TR>(leader, t_a0, t_d, xt_cur, idesc_pv_main, idesc_pv_tail, j > 0);  // dQ += dS K   /   dK += dS^T Q
+          commit(TR::kBarAccFull);
+          commit(TR::kBarXEmpty + s_cur);
           ++xcnt;
           if (more) {
-            issue_qk<TAIL, TR>(t_d, s_r + TR::kTileBytes, xt + TR::kTileBytes, idesc_qk, false);
-            tc_commit(bar(TR::kBarDFull));
-            if (j + 2 == J) tc_commit(bar(TR::kBarREmpty));
+            issue_qk<TAIL, TR>(leader, t_d, s_r + TR::kTileBytes, xt + TR::kTileBytes, idesc_qk, false);
+            commit(TR::kBarDFull);
+            if (j + 2 == J) commit(TR::kBarREmpty);
           }
         }
       }

@@ -13,16 +13,17 @@
 // running m (lazily updated max), l = sum P, mu = sum G; epilogue
 //   o = O / l,   to = T / l - (mu / l) o,   lse = ln2 * (m + log2 l).
 //
-// Warp roles (192 threads):
+// Warp roles (320 threads):
 //   warp 0     TMA producer: Q/dQ tile, then K/dK and V/dV blocks through two
 //              shared-memory rings; also owns the tensor-memory allocation
-//   warp 1     MMA issuer (one thread)
-//   warps 2-5  softmax + correction + epilogue; thread = query row,
-//              tensor-memory lane quarter = warp_id % 4
+//   warp 1     MMA issuer (warp-uniform control flow, one elected lane issues)
+//   warps 2-9  softmax + correction + epilogue, two warpgroups: thread = one query
+//              row (tensor-memory lane quarter = warp_id % 4) x one half of the
+//              128 score columns
 //
 // Tensor memory columns (fp32 accumulators, 128 lanes):
-//   [0,128)   S; P (16-bit, 64 columns) is written over it
-//   [128,256) dS; G is written over it      (plain forward: second S buffer)
+//   [0,128)   S; P (16-bit) is written over columns [0,32) and [64,96)
+//   [128,256) dS; G is written over it the same way (plain forward: second S buffer)
 //   [256, 256+DPAD)         O
 //   [256+DPAD, 256+2*DPAD)  T               (dual only)
 //
@@ -41,7 +42,8 @@ namespace dmf {
 
 constexpr int kBlockQ = 128;
 constexpr int kBlockKV = 128;
-constexpr int kFwdThreads = 192;
+constexpr int kFwdThreads = 320;       // TMA warp, MMA warp, two softmax warpgroups
+constexpr int kSoftmaxThreads = 256;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8
 
 // Codes written to the status word when a wait gives up: role * 100 + barrier.
@@ -87,10 +89,11 @@ struct FwdTraits {
   static constexpr int kTileSmem = kGroupBytes * (1 + kStagesK_) + kVGroupBytes * kStagesV_;
   // barriers
   static constexpr int kBarQFull = 0, kBarQEmpty = 1, kBarSFull = 2, kBarDSFull = 3, kBarPFull = 4,
-                       kBarGFull = 5, kBarAccFull = 6 /* and 7 */, kBarKFull = 8,
+                       kBarGFull = 5, kBarAccFull = 6 /* and 7 */, kBarXchg = 8, kBarKFull = 9,
                        kBarKEmpty = kBarKFull + kStagesK_, kBarVFull = kBarKEmpty + kStagesK_,
                        kBarVEmpty = kBarVFull + kStagesV_, kNumBars = kBarVEmpty + kStagesV_;
-  static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kTileSmem + kNumBars * 8 + 16;
+  static constexpr int kXchgBytes = 4096;  // row max / row sum exchange between the softmax groups
+  static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kTileSmem + kXchgBytes + kNumBars * 8 + 16;
   // tensor memory columns
   static constexpr uint32_t kColS = 0, kColDS = 128, kColO = 256, kColT = 256 + kDPad;
   static constexpr uint32_t kTmemCols = 512;
@@ -99,17 +102,17 @@ struct FwdTraits {
   static constexpr uint32_t kTailRowBytes = 2 * TAIL;
 };
 
-// ---- MMA issue helpers (one thread) ------------------------------------------
+// ---- MMA issue helpers: executed by the whole MMA warp, the instruction itself by its leader lane ----
 
 // acc[128 x 128] (+)= A[128 x D] * B[128 x D]^T, both operands K-major in shared memory.
 template <int TAIL, typename TR>
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile,
+__device__ __forceinline__ void issue_qk(bool leader, uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile,
                                          uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < 4; ++kk) {
     const uint64_t ad = make_smem_desc(a_tile + kk * 32, 16, 1024, kSwizzle128);
     const uint64_t bd = make_smem_desc(b_tile + kk * 32, 16, 1024, kSwizzle128);
-    mma_ss(d_tmem, ad, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
+    if (leader) mma_ss(d_tmem, ad, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 #pragma unroll
   for (int kk = 0; kk < TAIL / 16; ++kk) {
@@ -117,37 +120,38 @@ __device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t a_tile, uint3
                                        TR::kTailSwizzle);
     const uint64_t bd = make_smem_desc(b_tile + TR::kMainBytes + kk * 32, 16, 8 * TR::kTailRowBytes,
                                        TR::kTailSwizzle);
-    mma_ss(d_tmem, ad, bd, idesc, 1u);
+    if (leader) mma_ss(d_tmem, ad, bd, idesc, 1u);
   }
 }
 
 // acc[128 x DPAD] (+)= A[128 x 128] * V[128 x DPAD]; A is 16-bit in tensor memory
 // (two elements per column), V is MN-major (row = kv index, D contiguous) in shared memory.
 template <int TAIL, typename TR>
-__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t a_tmem, uint32_t v_tile,
+__device__ __forceinline__ void issue_pv(bool leader, uint32_t d_tmem, uint32_t a_tmem, uint32_t v_tile,
                                          uint32_t idesc_main, uint32_t idesc_tail, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < kBlockKV / 16; ++kk) {
     const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
     const uint64_t bd = make_smem_desc(v_tile + kk * (16 * 128), 8192, 1024, kSwizzle128);
-    mma_ts(d_tmem, a_tmem + kk * 8, bd, idesc_main, acc);
+    if (leader) mma_ts(d_tmem, a_tmem + kk * 8, bd, idesc_main, acc);
     if constexpr (TAIL > 0) {
       const uint64_t bt = make_smem_desc(v_tile + TR::kMainBytes + kk * (16 * TR::kTailRowBytes),
                                          TR::kTailBytes, 8 * TR::kTailRowBytes, TR::kTailSwizzle);
-      mma_ts(d_tmem + 64, a_tmem + kk * 8, bt, idesc_tail, acc);
+      if (leader) mma_ts(d_tmem + 64, a_tmem + kk * 8, bt, idesc_tail, acc);
     }
   }
 }
 
 // Same product with V stored as 64-byte-swizzled atoms of 32 columns: one MMA of N = DPAD per K-step.
 template <typename TR>
-__device__ __forceinline__ void issue_pv_atoms(uint32_t d_tmem, uint32_t a_tmem, uint32_t v_tile,
+__device__ __forceinline__ void issue_pv_atoms(bool leader, uint32_t d_tmem, uint32_t a_tmem, uint32_t v_tile,
                                                uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < kBlockKV / 16; ++kk) {
     // leading-dim offset = next 32-column atom, stride offset = next group of 8 kv rows
     const uint64_t bd = make_smem_desc(v_tile + kk * (16 * 64), TR::kVAtomBytes, 8 * 64, kSwizzle64);
-    mma_ts(d_tmem, a_tmem + kk * 8, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
+    // P / G columns: k-steps 0-3 sit in columns [0,32), k-steps 4-7 in [64,96) (one half per softmax group)
+    if (leader) mma_ts(d_tmem, a_tmem + (kk >> 2) * 64 + (kk & 3) * 8, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 
@@ -166,7 +170,8 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   const uint32_t s_q = smem_u32(smem);
   const uint32_t s_k = s_q + TR::kGroupBytes;
   const uint32_t s_v = s_k + TR::kStagesK_ * TR::kGroupBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TR::kTileSmem);
+  float* xchg = reinterpret_cast<float*>(smem + TR::kTileSmem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TR::kTileSmem + TR::kXchgBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + TR::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
@@ -179,8 +184,8 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < TR::kNumBars; ++i) {
-      const bool softmax_arrives = (i == TR::kBarPFull || i == TR::kBarGFull);  // kBarGFull == kBarPFull + 1
-      mbar_init(bar(i), softmax_arrives ? 128u : 1u);
+      const bool softmax_arrives = (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarXchg);
+      mbar_init(bar(i), softmax_arrives ? static_cast<uint32_t>(kSoftmaxThreads) : 1u);
     }
     fence_mbar_init();
   }
@@ -255,7 +260,11 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     }
   } else if (warp == 1) {
     // ============================ MMA issuer ================================
-    if (lane == 0) {
+    // The whole warp runs the loops and waits (warp-uniform control flow keeps descriptors in
+    // uniform registers); only the elected lane executes tcgen05.mma / tcgen05.commit.
+    {
+      const bool leader = elect_one();
+      auto commit = [&](int b_) { if (leader) tc_commit(bar(b_)); };
       constexpr uint32_t idesc_qk = make_idesc(kBf16, false, false, 128, 128);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, false, true, 128, DPAD);
       const uint32_t t_s = tmem + TR::kColS, t_ds = tmem + TR::kColDS;
@@ -263,7 +272,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       uint32_t kcnt = 0, vcnt = 0, tcnt = 0, pcnt = 0, gcnt = 0, scnt = 0;
       bool ok = true;
       auto wait = [&](int b_, uint32_t parity) -> bool {
-        return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_);
+        return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_));
       };
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcnt) {
         ok = wait(TR::kBarQFull, tcnt & 1u);
@@ -276,14 +285,14 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           if (!ok) break;
           tc_fence_after_sync();
           uint32_t kt = s_k + sk * TR::kGroupBytes;
-          issue_qk<TAIL, TR>(t_s, s_q, kt, idesc_qk, false);
-          tc_commit(bar(TR::kBarSFull));
-          issue_qk<TAIL, TR>(t_ds, s_q + TR::kTileBytes, kt, idesc_qk, false);
-          issue_qk<TAIL, TR>(t_ds, s_q, kt + TR::kTileBytes, idesc_qk, true);
-          tc_commit(bar(TR::kBarDSFull));
-          tc_commit(bar(TR::kBarKEmpty + sk));
+          issue_qk<TAIL, TR>(leader, t_s, s_q, kt, idesc_qk, false);
+          commit(TR::kBarSFull);
+          issue_qk<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, kt, idesc_qk, false);
+          issue_qk<TAIL, TR>(leader, t_ds, s_q, kt + TR::kTileBytes, idesc_qk, true);
+          commit(TR::kBarDSFull);
+          commit(TR::kBarKEmpty + sk);
           ++kcnt;
-          if (num_kv_blocks == 1) tc_commit(bar(TR::kBarQEmpty));
+          if (num_kv_blocks == 1) commit(TR::kBarQEmpty);
           for (int j = 0; j < num_kv_blocks; ++j) {
             const uint32_t sv = vcnt % TR::kStagesV_;
             const uint32_t vt = s_v + sv * TR::kVGroupBytes;
@@ -293,8 +302,8 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             if (!ok) break;
             ++pcnt;
             tc_fence_after_sync();
-            issue_pv_atoms<TR>(t_o, t_s, vt, idesc_pv, j > 0);                    // O += P V
-            issue_pv_atoms<TR>(t_t, t_s, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
+            issue_pv_atoms<TR>(leader, t_o, t_s, vt, idesc_pv, j > 0);                    // O += P V
+            issue_pv_atoms<TR>(leader, t_t, t_s, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
             const bool more = (j + 1 < num_kv_blocks);
             if (more) {
               sk = kcnt % TR::kStagesK_;
@@ -302,24 +311,24 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
               if (!ok) break;
               tc_fence_after_sync();
               kt = s_k + sk * TR::kGroupBytes;
-              issue_qk<TAIL, TR>(t_s, s_q, kt, idesc_qk, false);  // S of the next block (over P: issued after its readers)
-              tc_commit(bar(TR::kBarSFull));
+              issue_qk<TAIL, TR>(leader, t_s, s_q, kt, idesc_qk, false);  // S of the next block (over P: issued after its readers)
+              commit(TR::kBarSFull);
             }
             ok = wait(TR::kBarGFull, gcnt & 1u);
             if (!ok) break;
             ++gcnt;
             tc_fence_after_sync();
-            issue_pv_atoms<TR>(t_t, t_ds, vt, idesc_pv, true);  // T += G V
-            tc_commit(bar(TR::kBarAccFull));
-            tc_commit(bar(TR::kBarVEmpty + sv));
+            issue_pv_atoms<TR>(leader, t_t, t_ds, vt, idesc_pv, true);  // T += G V
+            commit(TR::kBarAccFull);
+            commit(TR::kBarVEmpty + sv);
             ++vcnt;
             if (more) {
-              issue_qk<TAIL, TR>(t_ds, s_q + TR::kTileBytes, kt, idesc_qk, false);
-              issue_qk<TAIL, TR>(t_ds, s_q, kt + TR::kTileBytes, idesc_qk, true);
-              tc_commit(bar(TR::kBarDSFull));
-              tc_commit(bar(TR::kBarKEmpty + sk));
+              issue_qk<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, kt, idesc_qk, false);
+              issue_qk<TAIL, TR>(leader, t_ds, s_q, kt + TR::kTileBytes, idesc_qk, true);
+              commit(TR::kBarDSFull);
+              commit(TR::kBarKEmpty + sk);
               ++kcnt;
-              if (j + 2 == num_kv_blocks) tc_commit(bar(TR::kBarQEmpty));
+              if (j + 2 == num_kv_blocks) commit(TR::kBarQEmpty);
             }
           }
         } else {
@@ -331,21 +340,21 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             const uint32_t sk = kcnt % TR::kStagesK_;
             if (!wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK_) & 1u)) return false;
             tc_fence_after_sync();
-            issue_qk<TAIL, TR>((scnt & 1u) ? t_ds : t_s, s_q, s_k + sk * TR::kGroupBytes, idesc_qk, false);
-            tc_commit(bar(TR::kBarSFull + (scnt & 1u)));
-            tc_commit(bar(TR::kBarKEmpty + sk));
+            issue_qk<TAIL, TR>(leader, (scnt & 1u) ? t_ds : t_s, s_q, s_k + sk * TR::kGroupBytes, idesc_qk, false);
+            commit(TR::kBarSFull + (scnt & 1u));
+            commit(TR::kBarKEmpty + sk);
             ++kcnt;
             ++scnt;
             return true;
           };
           ok = issue_s();
           if (!ok) break;
-          if (num_kv_blocks == 1) tc_commit(bar(TR::kBarQEmpty));
+          if (num_kv_blocks == 1) commit(TR::kBarQEmpty);
           for (int j = 0; j < num_kv_blocks; ++j) {
             if (j + 1 < num_kv_blocks) {
               ok = issue_s();
               if (!ok) break;
-              if (j + 2 == num_kv_blocks) tc_commit(bar(TR::kBarQEmpty));
+              if (j + 2 == num_kv_blocks) commit(TR::kBarQEmpty);
             }
             const uint32_t sv = vcnt % TR::kStagesV_;
             ok = wait(TR::kBarVFull + sv, (vcnt / TR::kStagesV_) & 1u);
@@ -353,10 +362,10 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             ok = wait(TR::kBarPFull + (pcnt & 1u), (pcnt >> 1) & 1u);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_pv_atoms<TR>(t_o, (pcnt & 1u) ? t_ds : t_s, s_v + sv * TR::kVGroupBytes, idesc_pv, j > 0);
-            tc_commit(bar(TR::kBarAccFull + (pcnt & 1u)));
+            issue_pv_atoms<TR>(leader, t_o, (pcnt & 1u) ? t_ds : t_s, s_v + sv * TR::kVGroupBytes, idesc_pv, j > 0);
+            commit(TR::kBarAccFull + (pcnt & 1u));
             ++pcnt;
-            tc_commit(bar(TR::kBarVEmpty + sv));
+            commit(TR::kBarVEmpty + sv);
             ++vcnt;
           }
         }
@@ -364,13 +373,23 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     }
   } else {
     // ===================== softmax / correction / epilogue ==================
-    const int quarter = warp & 3;               // tensor-memory lane quarter this warp may touch
-    const int row = quarter * 32 + lane;        // query row inside the tile
+    // Two warpgroups (warps 2-5 and 6-9).  A thread owns one query row (tensor-memory lane
+    // = 32 * (warp % 4) + lane) and one half of the 128 score columns: group g reads S / dS
+    // columns [64g, 64g+64) and writes its 16-bit P / G back over the first 32 of those columns
+    // (so no thread ever overwrites a column another thread still has to read).  The row max and,
+    // in the epilogue, the row sums are combined through shared memory.
+    const int grp = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t t_s = tmem + lane_base + TR::kColS, t_ds = tmem + lane_base + TR::kColDS;
+    const uint32_t col0 = 64u * static_cast<uint32_t>(grp);
+    const uint32_t t_s = tmem + lane_base + TR::kColS + col0, t_ds = tmem + lane_base + TR::kColDS + col0;
     const uint32_t t_o = tmem + lane_base + TR::kColO;
     const float sl2 = p.scale_log2e;
+    float* xmax = xchg;         // [block parity][group][row]
+    float* xsum = xchg + 512;   // [l | mu][group][row]
     uint32_t gblk = 0;  // blocks processed so far by this CTA (all tiles)
+    uint32_t xuse = 0;  // uses of the exchange barrier
     bool ok = true;
     // warp-uniform result: the warp-wide votes and .sync.aligned instructions below need all 32 lanes
     auto wait = [&](int b_, uint32_t parity) -> bool {
@@ -385,11 +404,19 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     auto wait_acc = [&](uint32_t blk) -> bool {
       return kDual ? wait(TR::kBarAccFull, blk & 1u) : wait(TR::kBarAccFull + (blk & 1u), (blk >> 1) & 1u);
     };
+    // All 256 softmax threads meet (bounded, like every other wait); shared-memory writes made
+    // before it are visible after it.
+    auto exchange = [&]() -> bool {
+      mbar_arrive(bar(TR::kBarXchg));
+      const bool r_ = wait(TR::kBarXchg, xuse & 1u);
+      ++xuse;
+      return r_;
+    };
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
       const int bh = tile / p.num_q_tiles;
       const int q0 = (tile % p.num_q_tiles) * kBlockQ;
       const int b = bh / p.heads, h = bh % p.heads;
-      float m_used = -CUDART_INF_F, l = 0.f, mu = 0.f;
+      float m_used = -CUDART_INF_F, l = 0.f, mu = 0.f;  // l, mu: this thread's columns only
       for (int j = 0; j < num_kv_blocks; ++j, ++gblk) {
         // ---- part 1: S -> P ------------------------------------------------
         const uint32_t buf = kDual ? 0u : (gblk & 1u);
@@ -397,13 +424,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t t_sb = buf ? t_ds : t_s;
-        uint32_t r[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_x32(t_sb + c * 32, r[c]);
+        uint32_t r[2][32];
+        tmem_ld_x32(t_sb, r[0]);
+        tmem_ld_x32(t_sb + 32, r[1]);
         tmem_wait_ld();
         float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             mx0 = max3(mx0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
@@ -412,7 +439,12 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             mx3 = max3(mx3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
           }
         }
-        const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+        const float m_loc = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        float* xm = xmax + (gblk & 1u) * 256;
+        xm[grp * 128 + row] = m_loc;
+        ok = exchange();
+        if (!ok) break;
+        const float m_blk = fmaxf(m_loc, xm[(1 - grp) * 128 + row]) * sl2;
         if (j == 0) {
           m_used = m_blk;
         } else {
@@ -428,7 +460,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             mu *= alpha;
             constexpr int kAccCols = kDual ? 2 * DPAD : DPAD;
 #pragma unroll 1
-            for (int c = 0; c < kAccCols / 16; ++c) {
+            for (int c = grp; c < kAccCols / 16; c += 2) {  // the two groups share the columns
               uint32_t a[16];
               tmem_ld_x16(t_o + c * 16, a);
               tmem_wait_ld();
@@ -443,7 +475,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         const uint64_t sl2_2 = pack_f2(sl2, sl2), neg_m2 = pack_f2(-m_used, -m_used);
         uint64_t la = pack_f2(0.f, 0.f), lb = la;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             float x0, x1, x2, x3;
@@ -464,7 +496,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           l += s0 + s1;
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i)
@@ -482,17 +514,19 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           tc_fence_after_sync();
           const uint64_t scale2 = pack_f2(p.scale, p.scale);
           uint64_t mua = pack_f2(0.f, 0.f), mub = mua;
+          uint32_t d[2][32];
+          tmem_ld_x32(t_ds, d[0]);
+          tmem_ld_x32(t_ds + 32, d[1]);
+          tmem_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t d[32];
-            tmem_ld_x32(t_ds + c * 32, d);
-            tmem_wait_ld();
+          for (int c = 0; c < 2; ++c) {
             uint32_t pk[16];
 #pragma unroll
             for (int i = 0; i < 16; i += 2) {
-              const uint64_t ga = mul2(pack_u2(r[c][2 * i], r[c][2 * i + 1]), mul2(pack_u2(d[2 * i], d[2 * i + 1]), scale2));
+              const uint64_t ga = mul2(pack_u2(r[c][2 * i], r[c][2 * i + 1]),
+                                       mul2(pack_u2(d[c][2 * i], d[c][2 * i + 1]), scale2));
               const uint64_t gb = mul2(pack_u2(r[c][2 * i + 2], r[c][2 * i + 3]),
-                                       mul2(pack_u2(d[2 * i + 2], d[2 * i + 3]), scale2));
+                                       mul2(pack_u2(d[c][2 * i + 2], d[c][2 * i + 3]), scale2));
               mua = add2(mua, ga);
               mub = add2(mub, gb);
               float g0, g1, g2, g3;
@@ -518,13 +552,20 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       ok = wait_acc(gblk - 1u);
       if (!ok) break;
       tc_fence_after_sync();
-      const float inv_l = 1.f / l;
-      const float mu_n = mu * inv_l;
+      xsum[grp * 128 + row] = l;
+      xsum[256 + grp * 128 + row] = mu;
+      ok = exchange();
+      if (!ok) break;
+      const float l_tot = l + xsum[(1 - grp) * 128 + row];
+      const float mu_tot = mu + xsum[256 + (1 - grp) * 128 + row];
+      const float inv_l = 1.f / l_tot;
+      const float mu_n = mu_tot * inv_l;
       const int64_t lq = q0 + row;
       T* o_row = reinterpret_cast<T*>(p.o) + b * p.o_sb + lq * p.o_sl + h * p.o_sh;
       T* to_row = kDual ? reinterpret_cast<T*>(p.to) + b * p.to_sb + lq * p.to_sl + h * p.to_sh : nullptr;
 #pragma unroll
       for (int c = 0; c < DPAD / 16; ++c) {
+        if ((c & 1) != grp) continue;  // the two groups alternate 16-column chunks
         uint32_t a[16], t[16];
         tmem_ld_x16(t_o + c * 16, a);
         if constexpr (kDual) tmem_ld_x16(t_o + DPAD + c * 16, t);
@@ -543,16 +584,17 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         }
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          const int col0 = c * 16 + hh * 8;
-          if (col0 < p.head_dim) {
-            *reinterpret_cast<uint4*>(o_row + col0) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
+          const int cc = c * 16 + hh * 8;
+          if (cc < p.head_dim) {
+            *reinterpret_cast<uint4*>(o_row + cc) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
             if constexpr (kDual)
-              *reinterpret_cast<uint4*>(to_row + col0) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
+              *reinterpret_cast<uint4*>(to_row + cc) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
           }
         }
       }
-      p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seqlen_q + lq] =
-          (m_used + __log2f(l)) * 0.6931471805599453f;
+      if (grp == 0)
+        p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seqlen_q + lq] =
+            (m_used + __log2f(l_tot)) * 0.6931471805599453f;
       // the accumulator reads above must be complete before the next tile's first MMA overwrites O / T
       tc_fence_before_sync();
     }

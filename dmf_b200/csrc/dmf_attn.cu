@@ -257,7 +257,7 @@ int launch_bwd_inst(const BwdParams& p, int grid, cudaStream_t stream) {
     (void)cudaGetLastError();
     return DMF_ATTN_ERR_LAUNCH;
   }
-  kernel<<<grid, kFwdThreads, TR::kSmemBytes, stream>>>(p);
+  kernel<<<grid, kBwdThreads, TR::kSmemBytes, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
 }
 

@@ -53,29 +53,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Upper limit of any single device-side wait.  When it runs out the waiting
-// thread records which wait gave up, raises the CTA-wide abort flag and the
-// kernel unwinds (frees its tensor memory, returns normally).
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// Upper limit of any single device-side wait, in SM clock cycles (about 2 s at 2 GHz).  When it
+// runs out the waiting thread records which wait gave up, raises the CTA-wide abort flag and the
+// kernel unwinds (frees its tensor memory, returns normally).  The limit is measured with the
+// SM-local cycle counter: %globaltimer costs several hundred nanoseconds per read, which on
+// the hot path (one read per wait that does not succeed at once) dominated the whole kernel.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 // Bounded mbarrier wait.  `abort_flag` is a CTA-shared int that any role sets
 // when its own wait ran out; every other wait then returns false promptly.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int32_t* status_word, int32_t code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
+  long long t0 = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
+    if ((++spins & 255u) == 0u) {  // bookkeeping only every 256 unsuccessful polls
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
         *abort_flag = 1;
         if (status_word != nullptr) atomicCAS(status_word, 0, code);
         return false;
@@ -188,6 +186,21 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[
       "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
       "r"(r[15])
       : "memory");
+}
+
+// One lane of a converged warp (the same lane every time).  Code that issues tcgen05.mma should
+// run warp-uniformly and predicate only the instruction itself on this, so that descriptors
+// and addresses stay in uniform registers instead of being moved there per instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 // ----------------------------------------------------------------------------
