@@ -118,7 +118,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < TR::kNumBars; ++i)
-      mbar_init(bar(i), (i == TR::kBarPFull || i == TR::kBarGFull) ? 128u : 1u);
+      mbar_init(bar(i), (i == TR::kBarPFull || i == TR::kBarGFull) ? 4u : 1u);  // one arrival per softmax warp
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -179,7 +179,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     // ============================ MMA issuer ================================
     {
       const bool leader = elect_one();
-      auto commit = [&](int b_) { if (leader) tc_commit(bar(b_)); };
+      auto commit = [&](int b_) { tc_commit(bar(b_), leader); };
       constexpr uint32_t idesc_qk = make_idesc(kBf16, false, false, 128, 128);
       constexpr uint32_t idesc_pv_main = make_idesc(kBf16, false, true, 128, 64);
       constexpr uint32_t idesc_pv_tail = make_idesc(kBf16, false, true, 128, TAIL > 0 ? TAIL : 16);
@@ -188,7 +188,8 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       uint32_t xcnt = 0, tcnt = 0, pcnt = 0, gcnt = 0;
       bool ok = true;
       auto wait = [&](int b_, uint32_t parity) -> bool {
-        return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_));
+        // no vote: a lane can only disagree once the abort flag is up, and nothing below needs convergence
+        return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_);
       };
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcnt) {
         ok = wait(TR::kBarRFull, tcnt & 1u);
@@ -321,7 +322,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
           tmem_wait_st();
         }
         tc_fence_before_sync();
-        mbar_arrive(bar(TR::kBarPFull));  // DQ: S has been read;  DKV: P^T is in tensor memory
+        mbar_arrive_warp(bar(TR::kBarPFull));  // DQ: S has been read;  DKV: P^T is in tensor memory
 
         // ---- part 2: dS = P * (dP - delta) -----------------------------------
         ok = wait(TR::kBarDFull, gblk & 1u);
@@ -351,7 +352,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(bar(TR::kBarGFull));
+        mbar_arrive_warp(bar(TR::kBarGFull));
       }
       if (!ok) break;
       // ---- epilogue --------------------------------------------------------

@@ -22,10 +22,11 @@
 //              128 score columns
 //
 // Tensor memory columns (fp32 accumulators, 128 lanes):
-//   [0,128)   S; P (16-bit) is written over columns [0,32) and [64,96)
-//   [128,256) dS; G is written over it the same way (plain forward: second S buffer)
-//   [256, 256+DPAD)         O
-//   [256+DPAD, 256+2*DPAD)  T               (dual only)
+//   [0,128)   S
+//   [128,256) dS; G (16-bit) is written over its columns [0,32) and [64,96)
+//   [256,320) P (16-bit), dual pass with DPAD <= 96; otherwise P is written over S like G over dS
+//             (plain forward: [128,256) is the second S buffer)
+//   then O (DPAD columns) and, dual only, T (DPAD columns)
 //
 // Head dim D is handled as a 64-column main part (128-byte swizzle) plus a tail
 // of TAIL in {0,16,32,64} columns (swizzle of 2*TAIL bytes); columns past D in
@@ -43,7 +44,7 @@ namespace dmf {
 constexpr int kBlockQ = 128;
 constexpr int kBlockKV = 128;
 constexpr int kFwdThreads = 320;       // TMA warp, MMA warp, two softmax warpgroups
-constexpr int kSoftmaxThreads = 256;
+constexpr int kSoftmaxWarps = 8;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8
 
 // Codes written to the status word when a wait gives up: role * 100 + barrier.
@@ -89,13 +90,19 @@ struct FwdTraits {
   static constexpr int kTileSmem = kGroupBytes * (1 + kStagesK_) + kVGroupBytes * kStagesV_;
   // barriers
   static constexpr int kBarQFull = 0, kBarQEmpty = 1, kBarSFull = 2, kBarDSFull = 3, kBarPFull = 4,
-                       kBarGFull = 5, kBarAccFull = 6 /* and 7 */, kBarXchg = 8, kBarKFull = 9,
+                       kBarGFull = 5, kBarAccFull = 6 /* and 7 */, kBarXchg = 8, kBarSEmpty = 9, kBarPEmpty = 10,
+                       kBarKFull = 11,
                        kBarKEmpty = kBarKFull + kStagesK_, kBarVFull = kBarKEmpty + kStagesK_,
                        kBarVEmpty = kBarVFull + kStagesV_, kNumBars = kBarVEmpty + kStagesV_;
   static constexpr int kXchgBytes = 4096;  // row max / row sum exchange between the softmax groups
   static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kTileSmem + kXchgBytes + kNumBars * 8 + 16;
   // tensor memory columns
-  static constexpr uint32_t kColS = 0, kColDS = 128, kColO = 256, kColT = 256 + kDPad;
+  // Dual pass with room in tensor memory (DPAD <= 96): P gets columns of its own, so S of the
+  // next block can be issued as soon as the softmax has read the current S, instead of behind the
+  // P V products that read P.  Otherwise P is written over S.
+  static constexpr bool kSepP = kDual && (kDPad <= 96);
+  static constexpr uint32_t kColS = 0, kColDS = 128, kColP = 256, kColO = kSepP ? 320 : 256,
+                            kColT = kColO + kDPad;
   static constexpr uint32_t kTmemCols = 512;
   // swizzle of the tail part
   static constexpr uint32_t kTailSwizzle = TAIL == 64 ? kSwizzle128 : (TAIL == 32 ? kSwizzle64 : kSwizzle32);
@@ -112,7 +119,7 @@ __device__ __forceinline__ void issue_qk(bool leader, uint32_t d_tmem, uint32_t 
   for (int kk = 0; kk < 4; ++kk) {
     const uint64_t ad = make_smem_desc(a_tile + kk * 32, 16, 1024, kSwizzle128);
     const uint64_t bd = make_smem_desc(b_tile + kk * 32, 16, 1024, kSwizzle128);
-    if (leader) mma_ss(d_tmem, ad, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
+    mma_ss(d_tmem, ad, bd, idesc, (accumulate || kk > 0) ? 1u : 0u, leader);
   }
 #pragma unroll
   for (int kk = 0; kk < TAIL / 16; ++kk) {
@@ -120,7 +127,7 @@ __device__ __forceinline__ void issue_qk(bool leader, uint32_t d_tmem, uint32_t 
                                        TR::kTailSwizzle);
     const uint64_t bd = make_smem_desc(b_tile + TR::kMainBytes + kk * 32, 16, 8 * TR::kTailRowBytes,
                                        TR::kTailSwizzle);
-    if (leader) mma_ss(d_tmem, ad, bd, idesc, 1u);
+    mma_ss(d_tmem, ad, bd, idesc, 1u, leader);
   }
 }
 
@@ -133,25 +140,27 @@ __device__ __forceinline__ void issue_pv(bool leader, uint32_t d_tmem, uint32_t 
   for (int kk = 0; kk < kBlockKV / 16; ++kk) {
     const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
     const uint64_t bd = make_smem_desc(v_tile + kk * (16 * 128), 8192, 1024, kSwizzle128);
-    if (leader) mma_ts(d_tmem, a_tmem + kk * 8, bd, idesc_main, acc);
+    mma_ts(d_tmem, a_tmem + kk * 8, bd, idesc_main, acc, leader);
     if constexpr (TAIL > 0) {
       const uint64_t bt = make_smem_desc(v_tile + TR::kMainBytes + kk * (16 * TR::kTailRowBytes),
                                          TR::kTailBytes, 8 * TR::kTailRowBytes, TR::kTailSwizzle);
-      if (leader) mma_ts(d_tmem + 64, a_tmem + kk * 8, bt, idesc_tail, acc);
+      mma_ts(d_tmem + 64, a_tmem + kk * 8, bt, idesc_tail, acc, leader);
     }
   }
 }
 
 // Same product with V stored as 64-byte-swizzled atoms of 32 columns: one MMA of N = DPAD per K-step.
-template <typename TR>
+// kSplitA: the 16-bit A operand was written over a 128-column fp32 buffer by the two softmax
+// groups, k-steps 0-3 in columns [0,32) and k-steps 4-7 in [64,96); otherwise it is contiguous.
+template <typename TR, bool kSplitA>
 __device__ __forceinline__ void issue_pv_atoms(bool leader, uint32_t d_tmem, uint32_t a_tmem, uint32_t v_tile,
                                                uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < kBlockKV / 16; ++kk) {
     // leading-dim offset = next 32-column atom, stride offset = next group of 8 kv rows
     const uint64_t bd = make_smem_desc(v_tile + kk * (16 * 64), TR::kVAtomBytes, 8 * 64, kSwizzle64);
-    // P / G columns: k-steps 0-3 sit in columns [0,32), k-steps 4-7 in [64,96) (one half per softmax group)
-    if (leader) mma_ts(d_tmem, a_tmem + (kk >> 2) * 64 + (kk & 3) * 8, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
+    const uint32_t a_col = kSplitA ? (kk >> 2) * 64 + (kk & 3) * 8 : kk * 8;
+    mma_ts(d_tmem, a_tmem + a_col, bd, idesc, (accumulate || kk > 0) ? 1u : 0u, leader);
   }
 }
 
@@ -184,8 +193,9 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < TR::kNumBars; ++i) {
-      const bool softmax_arrives = (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarXchg);
-      mbar_init(bar(i), softmax_arrives ? static_cast<uint32_t>(kSoftmaxThreads) : 1u);
+      const bool softmax_arrives =
+          (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarXchg || i == TR::kBarSEmpty);
+      mbar_init(bar(i), softmax_arrives ? static_cast<uint32_t>(kSoftmaxWarps) : 1u);  // one arrival per warp
     }
     fence_mbar_init();
   }
@@ -264,7 +274,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     // uniform registers); only the elected lane executes tcgen05.mma / tcgen05.commit.
     {
       const bool leader = elect_one();
-      auto commit = [&](int b_) { if (leader) tc_commit(bar(b_)); };
+      auto commit = [&](int b_) { tc_commit(bar(b_), leader); };
       constexpr uint32_t idesc_qk = make_idesc(kBf16, false, false, 128, 128);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, false, true, 128, DPAD);
       const uint32_t t_s = tmem + TR::kColS, t_ds = tmem + TR::kColDS;
@@ -272,21 +282,32 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       uint32_t kcnt = 0, vcnt = 0, tcnt = 0, pcnt = 0, gcnt = 0, scnt = 0;
       bool ok = true;
       auto wait = [&](int b_, uint32_t parity) -> bool {
-        return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_));
+        // no vote: a lane can only disagree once the abort flag is up, and nothing below needs convergence
+        return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_);
       };
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcnt) {
         ok = wait(TR::kBarQFull, tcnt & 1u);
         if (!ok) break;
         tc_fence_after_sync();
         if constexpr (kDual) {
+          constexpr bool kSepP = TR::kSepP;
+          const uint32_t t_p = kSepP ? tmem + TR::kColP : t_s;
           // block 0: S and dS
           uint32_t sk = kcnt % TR::kStagesK_;
+          if constexpr (kSepP) {
+            // S is about to be overwritten: the softmax must have read the previous block's S
+            if (scnt > 0) {
+              ok = wait(TR::kBarSEmpty, (scnt - 1u) & 1u);
+              if (!ok) break;
+            }
+          }
           ok = wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK_) & 1u);
           if (!ok) break;
           tc_fence_after_sync();
           uint32_t kt = s_k + sk * TR::kGroupBytes;
           issue_qk<TAIL, TR>(leader, t_s, s_q, kt, idesc_qk, false);
           commit(TR::kBarSFull);
+          ++scnt;
           issue_qk<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, kt, idesc_qk, false);
           issue_qk<TAIL, TR>(leader, t_ds, s_q, kt + TR::kTileBytes, idesc_qk, true);
           commit(TR::kBarDSFull);
@@ -296,29 +317,49 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           for (int j = 0; j < num_kv_blocks; ++j) {
             const uint32_t sv = vcnt % TR::kStagesV_;
             const uint32_t vt = s_v + sv * TR::kVGroupBytes;
+            const bool more = (j + 1 < num_kv_blocks);
+            // S of the next block.  With a separate P buffer it goes first (the tensor pipe computes
+            // it while the softmax of this block runs); with P over S it must follow the readers of P.
+            auto issue_next_s = [&]() -> bool {
+              sk = kcnt % TR::kStagesK_;
+              if constexpr (kSepP) {
+                if (!wait(TR::kBarSEmpty, (scnt - 1u) & 1u)) return false;
+              }
+              if (!wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK_) & 1u)) return false;
+              tc_fence_after_sync();
+              kt = s_k + sk * TR::kGroupBytes;
+              issue_qk<TAIL, TR>(leader, t_s, s_q, kt, idesc_qk, false);
+              commit(TR::kBarSFull);
+              ++scnt;
+              return true;
+            };
+            if constexpr (kSepP) {
+              if (more) {
+                ok = issue_next_s();
+                if (!ok) break;
+              }
+            }
             ok = wait(TR::kBarVFull + sv, (vcnt / TR::kStagesV_) & 1u);
             if (!ok) break;
             ok = wait(TR::kBarPFull, pcnt & 1u);
             if (!ok) break;
             ++pcnt;
             tc_fence_after_sync();
-            issue_pv_atoms<TR>(leader, t_o, t_s, vt, idesc_pv, j > 0);                    // O += P V
-            issue_pv_atoms<TR>(leader, t_t, t_s, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
-            const bool more = (j + 1 < num_kv_blocks);
-            if (more) {
-              sk = kcnt % TR::kStagesK_;
-              ok = wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK_) & 1u);
-              if (!ok) break;
-              tc_fence_after_sync();
-              kt = s_k + sk * TR::kGroupBytes;
-              issue_qk<TAIL, TR>(leader, t_s, s_q, kt, idesc_qk, false);  // S of the next block (over P: issued after its readers)
-              commit(TR::kBarSFull);
+            issue_pv_atoms<TR, !kSepP>(leader, t_o, t_p, vt, idesc_pv, j > 0);                    // O += P V
+            issue_pv_atoms<TR, !kSepP>(leader, t_t, t_p, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
+            if constexpr (kSepP) {
+              commit(TR::kBarPEmpty);
+            } else {
+              if (more) {
+                ok = issue_next_s();
+                if (!ok) break;
+              }
             }
             ok = wait(TR::kBarGFull, gcnt & 1u);
             if (!ok) break;
             ++gcnt;
             tc_fence_after_sync();
-            issue_pv_atoms<TR>(leader, t_t, t_ds, vt, idesc_pv, true);  // T += G V
+            issue_pv_atoms<TR, true>(leader, t_t, t_ds, vt, idesc_pv, true);  // T += G V
             commit(TR::kBarAccFull);
             commit(TR::kBarVEmpty + sv);
             ++vcnt;
@@ -362,7 +403,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             ok = wait(TR::kBarPFull + (pcnt & 1u), (pcnt >> 1) & 1u);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_pv_atoms<TR>(leader, t_o, (pcnt & 1u) ? t_ds : t_s, s_v + sv * TR::kVGroupBytes, idesc_pv, j > 0);
+            issue_pv_atoms<TR, true>(leader, t_o, (pcnt & 1u) ? t_ds : t_s, s_v + sv * TR::kVGroupBytes, idesc_pv, j > 0);
             commit(TR::kBarAccFull + (pcnt & 1u));
             ++pcnt;
             commit(TR::kBarVEmpty + sv);
@@ -407,7 +448,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     // All 256 softmax threads meet (bounded, like every other wait); shared-memory writes made
     // before it are visible after it.
     auto exchange = [&]() -> bool {
-      mbar_arrive(bar(TR::kBarXchg));
+      mbar_arrive_warp(bar(TR::kBarXchg));
       const bool r_ = wait(TR::kBarXchg, xuse & 1u);
       ++xuse;
       return r_;
@@ -428,6 +469,10 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         tmem_ld_x32(t_sb, r[0]);
         tmem_ld_x32(t_sb + 32, r[1]);
         tmem_wait_ld();
+        if constexpr (TR::kSepP) {  // S is in registers: the MMA warp may overwrite it with the next block's S
+          tc_fence_before_sync();
+          mbar_arrive_warp(bar(TR::kBarSEmpty));
+        }
         float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -495,17 +540,27 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           unpack_f2(add2(la, lb), s0, s1);
           l += s0 + s1;
         }
+        uint32_t t_pst = t_sb;  // P over this thread's own S columns ...
+        if constexpr (TR::kSepP) {
+          // ... or into the P buffer, once the P V products of the previous block have read it
+          t_pst = tmem + lane_base + TR::kColP + 32u * static_cast<uint32_t>(grp);
+          if (gblk > 0) {
+            ok = wait(TR::kBarPEmpty, (gblk - 1u) & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+        }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             pk[i] = Pack2<T>::pack(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
-          tmem_st_x16(t_sb + c * 16, pk);
+          tmem_st_x16(t_pst + c * 16, pk);
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(bar(TR::kBarPFull + buf));
+        mbar_arrive_warp(bar(TR::kBarPFull + buf));
 
         if constexpr (kDual) {
           // ---- part 2: G = P * dS * scale, mu += rowsum(G) ------------------
@@ -544,7 +599,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           }
           tmem_wait_st();
           tc_fence_before_sync();
-          mbar_arrive(bar(TR::kBarGFull));
+          mbar_arrive_warp(bar(TR::kBarGFull));
         }
       }
       if (!ok) break;

@@ -34,6 +34,14 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// One arrival on behalf of a whole (converged) warp: the warp synchronises, which orders every
+// lane's earlier writes before lane 0's releasing arrive.  256 single-thread arrivals on one
+// barrier serialise on one shared-memory word; 8 warp arrivals do not.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
@@ -62,8 +70,10 @@ constexpr long long kWaitLimitCycles = 4000000000ll;
 
 // Bounded mbarrier wait.  `abort_flag` is a CTA-shared int that any role sets
 // when its own wait ran out; every other wait then returns false promptly.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* status_word, int32_t code) {
+// The first poll is inlined (a wait that is already satisfied costs one shared-memory
+// round trip); everything else lives in an out-of-line slow path.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int32_t* status_word, int32_t code) {
   uint32_t spins = 0;
   long long t0 = 0;
   while (true) {
@@ -80,6 +90,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
     }
   }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status_word, int32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
 }
 
 // ----------------------------------------------------------------------------
@@ -133,9 +149,15 @@ __device__ __forceinline__ void tmem_wait_st() {
 }
 
 // mbarrier arrive once every tcgen05 operation issued so far by this thread has completed.
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
+__device__ __forceinline__ void tc_commit(uint32_t bar, bool issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}"
+      ::"r"(bar), "r"(static_cast<uint32_t>(issue))
+      : "memory");
 }
 
 // 32 lanes x 32 bit, 32 / 16 consecutive columns: thread i of the warp gets row
@@ -234,29 +256,35 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn_major, bo
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
+// D[tmem] (+)= A[smem] * B[smem].  Executed by a whole warp; the instruction itself is
+// predicated on `issue`, which must be true in exactly one lane.  Keeping the predicate inside
+// the instruction (no branch around it) keeps the warp converged.
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
+                                       uint32_t idesc, uint32_t accumulate, bool issue) {
   asm volatile(
       "{\n\t"
-      ".reg .pred p;\n\t"
+      ".reg .pred p, q;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
       "}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate),
+      "r"(static_cast<uint32_t>(issue))
       : "memory");
 }
 
 // D[tmem] (+)= A[tmem] * B[smem]; A holds 16-bit elements packed two per column.
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
+                                       uint32_t idesc, uint32_t accumulate, bool issue) {
   asm volatile(
       "{\n\t"
-      ".reg .pred p;\n\t"
+      ".reg .pred p, q;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
       "}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate),
+      "r"(static_cast<uint32_t>(issue))
       : "memory");
 }
 
