@@ -332,19 +332,149 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_model(args):
+    """Whole-model configurations: C4 (training step, data parallel with an NCCL gradient
+    all-reduce) and C5 (4-step Euler sampling, sharded per rank, no collective)."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    from dmf_b200 import ops
+    from dmf_b200.harness import train as T
+    from dmf_b200.harness.model import build_dmft
+    from dmf_b200.harness.sampler import euler_sampler
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    warm = max(args.warmup, 3) if args.warmup != 10 else 3
+    steps = args.steps if args.steps != 200 else (5 if args.workload == "C4" else 10)
+
+    if args.workload == "C4":
+        global_batch, mb = 256, args.micro_batch
+        assert global_batch % (mb * world) == 0, "256 must be divisible by micro_batch * n_gpus"
+        n_micro = global_batch // (mb * world)
+        st = T.build_train_state(dev, name=args.model, input_size=32, dmf_depth=20, attn_func="fa3", seed=0)
+        gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
+        # the step's inputs start in pinned host memory: latents N(0,1), labels uniform
+        host = [(torch.randn(mb, 4, 32, 32, generator=gen).pin_memory(),
+                 torch.randint(0, 1000, (mb,), generator=gen).pin_memory()) for _ in range(n_micro)]
+        torch.manual_seed(rank)
+
+        def step():
+            batches = [(x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)) for x, y in host]
+            return T.train_step(st, batches)
+
+        units, metric, unit, scaling = global_batch, "dmft_xl2_train_images_per_s", "images/s", "strong"
+        desc = (f"{args.model} training step: FM forward + JVP forward + backward, bf16 autocast, global batch 256 = "
+                f"{world} GPU x {n_micro} micro-batches x {mb}, DDP gradient all-reduce, clip 1.0, fused AdamW, EMA")
+        h2d = sum(x.numel() * x.element_size() + y.numel() * y.element_size() for x, y in host)
+        d2h = 4
+    else:
+        per_gpu = 64
+        torch.manual_seed(0)
+        model = build_dmft(args.model, input_size=64, dmf_depth=20, use_logvar=False, num_classes=1000,
+                           attn_func="fa3", qk_norm=True).to(dev).to(torch.bfloat16).eval()
+        gen = torch.Generator(device="cpu").manual_seed(rank)   # per-rank seed, as generate.py:43
+        z_host = torch.randn(per_gpu, 4, 64, 64, generator=gen).to(torch.bfloat16).pin_memory()
+        y_host = torch.randint(0, 1000, (per_gpu,), generator=gen).pin_memory()
+        out_host = torch.empty(per_gpu, 4, 64, 64, dtype=torch.float64).pin_memory()
+
+        def step():
+            z, y = z_host.to(dev, non_blocking=True), y_host.to(dev, non_blocking=True)
+            x = euler_sampler(model, z, y, num_steps=4, shift=1.5, cfg_scale=1.0)
+            out_host.copy_(x, non_blocking=True)
+            return x
+
+        units, metric, unit, scaling = per_gpu * world, "dmft_xl2_sample_images_per_s", "images/s", "weak"
+        desc = (f"{args.model} 4-step Euler sampling at 512px (latent 4x64x64, shift 1.5, qk-norm, bf16 weights), "
+                f"{per_gpu} images per GPU, no VAE decode")
+        h2d = z_host.numel() * 2 + y_host.numel() * 8
+        d2h = out_host.numel() * 8
+
+    for _ in range(warm):
+        out = step()
+    sync_all()
+    sampler.active.set()
+    launches0 = ops.launch_count
+    e0.record(stream)
+    for _ in range(steps):
+        out = step()
+    e1.record(stream)
+    sync_all()
+    launches = ops.launch_count - launches0
+    sampler.active.clear()
+    sampler.stop()
+    ms_total = e0.elapsed_time(e1)
+    ops.check_device_status(dev)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / steps
+    value = units / (ms_step * 1e-3)
+    if rank == 0:
+        loss_val = float(out.float().mean().item()) if args.workload == "C4" else None
+        line = {
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {desc}", "weights": "random init (reference initialisation)",
+                       "attn_func": "fa3 -> dmf_b200 sm_100a kernels",
+                       "l2": "activations and weights far exceed the 126 MB L2"},
+            "roofline": None, "cpu_baseline": None,
+            # every step already starts from pinned host inputs and ends with a device-to-host read
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "api": "dmf_b200.harness train_step / euler_sampler"},
+            "gpu_launches": launches, "clocks": sampler.summary(),
+            "mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
+            **({"last_loss": loss_val} if loss_val is not None else {}),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=list(WORKLOADS), default="C3")
+    ap.add_argument("--workload", choices=list(WORKLOADS) + ["C4", "C5"], default="C3",
+                    help="C3/C2: attention JVP op (default C3, the bench line); C4: DMFT-XL/2 training step, "
+                         "global batch 256; C5: DMFT-XL/2 4-step Euler sampling at 512px, 64 images per GPU")
+    ap.add_argument("--micro-batch", type=int, default=32, help="C4: images per forward/backward pass")
+    ap.add_argument("--model", default="DMFT-XL/2", help="C4/C5: harness model name (smaller ones for smoke runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the per-GPU batch of the workload (profiling runs only; the bench line needs the default)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload in ("C4", "C5"):
+        if args.impl == "reference":
+            # whole-model CPU runs of DMFT-XL/2 take minutes per step; the CPU arm exists for the op (C2/C3)
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable":
+                                  "whole-model CPU baseline not provided; use --workload C3 for the op"}))
+            return
+        run_model(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

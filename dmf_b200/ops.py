@@ -25,6 +25,9 @@ from . import _lib
 
 _DTYPES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.FP16}
 
+# Kernel launches made through this module since import (a backward call launches two kernels).
+launch_count = 0
+
 # One int32 per device that kernels write to when a device-side wait runs out.
 _status_words: dict[int, torch.Tensor] = {}
 # DMF_ATTN_CHECK=1 reads the status word back after every call (synchronises; for tests and debugging).
@@ -103,6 +106,8 @@ def fwd_dual_raw(q, k, v, tq, tk, tv, scale: float):
         a.q, a.k, a.v, a.tq, a.tk, a.tv, a.o, a.to = (_t4(x) for x in (q, k, v, tq, tk, tv, o, to))
         a.lse = lse.data_ptr()
         _lib.check(_lib.load().dmf_attn_fwd_dual(C.byref(a)))
+        global launch_count
+        launch_count += 1
         if _CHECK_EVERY_CALL:
             check_device_status(q.device)
     return o, to, lse
@@ -122,6 +127,8 @@ def fwd_raw(q, k, v, scale: float):
         a.q, a.k, a.v, a.o = (_t4(x) for x in (q, k, v, o))
         a.lse = lse.data_ptr()
         _lib.check(_lib.load().dmf_attn_fwd(C.byref(a)))
+        global launch_count
+        launch_count += 1
         if _CHECK_EVERY_CALL:
             check_device_status(q.device)
     return o, lse
@@ -146,6 +153,8 @@ def bwd_raw(dout, q, k, v, o, lse, scale: float):
         a.lse = lse.data_ptr()
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws_bytes
         _lib.check(lib.dmf_attn_bwd(C.byref(a)))
+        global launch_count
+        launch_count += 2
         if _CHECK_EVERY_CALL:
             check_device_status(q.device)
     return dq, dk, dv

@@ -1,0 +1,81 @@
+"""Whole-model check on a GPU: the harness DMFT with attn_func='fa3' (the sm_100a kernels)
+against the same weights with attn_func='base' (naive attention), through forward,
+torch.func.jvp, the DMF loss and its backward; plus one train step and a sampler run."""
+
+import copy
+
+import pytest
+import torch
+
+from dmf_b200 import ops
+from dmf_b200.harness import train as T
+from dmf_b200.harness.loss import DMFLoss
+from dmf_b200.harness.model import DMFT
+from dmf_b200.harness.sampler import euler_sampler
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _pair(qk_norm):
+    torch.manual_seed(0)
+    kw = dict(input_size=32, patch_size=2, in_channels=4, hidden_size=144, depth=3, num_heads=2, dmf_depth=2,
+              use_logvar=True, num_classes=1000, qk_norm=qk_norm)   # 256 tokens, head dim 72
+    fa = DMFT(**kw, attn_func="fa3")
+    fa.initialize_weights(zero_init=False)   # zero-initialised gates would hide the attention output
+    base = DMFT(**kw, attn_func="base")
+    base.load_state_dict(fa.state_dict())
+    return fa.to(DEV), base.to(DEV)
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+
+
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_model_jvp_and_loss_gradients_match_base_attention(qk_norm):
+    fa, base = _pair(qk_norm)
+    g = torch.Generator(device=DEV).manual_seed(1)
+    x = torch.randn(4, 4, 32, 32, device=DEV, generator=g)
+    y = torch.randint(0, 1000, (4,), device=DEV, generator=g)
+    t = torch.rand(4, 1, 1, 1, device=DEV, generator=g)
+    r = t * torch.rand(4, 1, 1, 1, device=DEV, generator=g)
+    v = torch.randn(4, 4, 32, 32, device=DEV, generator=g)
+    outs = []
+    for m in (fa, base):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            (u, lv), (du, _) = torch.func.jvp(lambda a, b, c: m(a, b, c, y=y, return_logvar=True), (x, t, r),
+                                              (v, torch.ones_like(t), torch.zeros_like(r)))
+        outs.append((u, du))
+    assert _rel(outs[0][0], outs[1][0]) < 2e-2
+    assert _rel(outs[0][1], outs[1][1]) < 3e-2
+    grads = []
+    for m in (fa, base):
+        torch.manual_seed(5)
+        m.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss, _ = DMFLoss()(m, m, x, y)
+        loss.mean().backward()
+        grads.append((float(loss.mean()), m.blocks[0].attn.qkv.weight.grad.clone(), m.blocks[2].mlp.fc1.weight.grad.clone()))
+    assert abs(grads[0][0] - grads[1][0]) < 2e-2 * max(1.0, abs(grads[1][0]))
+    assert _rel(grads[0][1], grads[1][1]) < 5e-2
+    assert _rel(grads[0][2], grads[1][2]) < 5e-2
+    ops.check_device_status(DEV)
+
+
+def test_train_step_and_sampler_run():
+    st = T.build_train_state(DEV, name="DMFT-S/2", input_size=32, dmf_depth=8, attn_func="fa3", seed=0,
+                             zero_init=False)
+    before = copy.deepcopy(st.model.state_dict())
+    n0 = ops.launch_count
+    loss = T.train_step(st, [T.synthetic_batch(st, 4), T.synthetic_batch(st, 4)])
+    assert torch.isfinite(loss)
+    # per micro-batch: 12 plain forwards + 12 dual forwards + 24 backward calls of 2 kernels
+    assert ops.launch_count - n0 == 2 * (12 + 12 + 24 * 2)
+    assert any(not torch.equal(v, before[k]) for k, v in st.model.state_dict().items())
+    model = st.model.to(torch.bfloat16).eval()
+    z = torch.randn(4, 4, 32, 32, device=DEV, dtype=torch.bfloat16)
+    y = torch.randint(0, 1000, (4,), device=DEV)
+    out = euler_sampler(model, z, y, num_steps=4, shift=1.5)
+    assert out.shape == (4, 4, 32, 32) and out.dtype == torch.float64 and bool(torch.isfinite(out).all())
+    ops.check_device_status(DEV)
