@@ -65,7 +65,19 @@ struct FwdParams {
   int batch, heads, seqlen_q, seqlen_kv, head_dim;
   int num_q_tiles, num_tiles;
   float scale, scale_log2e;
+  // Sector alignment of head rows (only used for head_dim 72, whose rows are 4.5 sectors of 32 B):
+  // a row of (b, h) starts (align0 + b * align_b + h * align_h) mod 32 bytes into a sector.  When
+  // that is 16, boxes are started 8 columns early (the 8 columns read as zeros) so that every box
+  // begins on a sector boundary; otherwise each misaligned row drags in one or two extra sectors.
+  // {qk, v}: the contraction group q, k, tq, tk and the group v, tv; enable = 0 turns a group off.
+  int align_enable[2], align0[2], align_b[2], align_h[2];
 };
+
+// 8 when the rows of (b, h) start in the middle of a 32-byte sector and the group may be shifted.
+__device__ __forceinline__ int column_shift(const FwdParams& p, int grp, int b, int h) {
+  if (!p.align_enable[grp]) return 0;
+  return (((p.align0[grp] + b * p.align_b[grp] + h * p.align_h[grp]) & 31) == 16) ? 8 : 0;
+}
 
 template <int TAIL, bool kDual>
 struct FwdTraits {
@@ -224,13 +236,14 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         ok = mbar_wait(bar(TR::kBarQEmpty), (tcnt & 1u) ^ 1u, abort_flag, p.status_word,
                        kRoleProducer + TR::kBarQEmpty);
         if (!ok) break;
+        const int xqk = -column_shift(p, 0, b, h), xv = -column_shift(p, 1, b, h);
         mbar_arrive_expect_tx(bar(TR::kBarQFull), TR::kGroupBytes);
-        tma_load_4d(s_q, &p.q_main, bar(TR::kBarQFull), 0, q0, h, b);
-        if constexpr (TAIL > 0) tma_load_4d(s_q + TR::kMainBytes, &p.q_tail, bar(TR::kBarQFull), 64, q0, h, b);
+        tma_load_4d(s_q, &p.q_main, bar(TR::kBarQFull), xqk, q0, h, b);
+        if constexpr (TAIL > 0) tma_load_4d(s_q + TR::kMainBytes, &p.q_tail, bar(TR::kBarQFull), 64 + xqk, q0, h, b);
         if constexpr (kDual) {
-          tma_load_4d(s_q + TR::kTileBytes, &p.tq_main, bar(TR::kBarQFull), 0, q0, h, b);
+          tma_load_4d(s_q + TR::kTileBytes, &p.tq_main, bar(TR::kBarQFull), xqk, q0, h, b);
           if constexpr (TAIL > 0)
-            tma_load_4d(s_q + TR::kTileBytes + TR::kMainBytes, &p.tq_tail, bar(TR::kBarQFull), 64, q0, h, b);
+            tma_load_4d(s_q + TR::kTileBytes + TR::kMainBytes, &p.tq_tail, bar(TR::kBarQFull), 64 + xqk, q0, h, b);
         }
         for (int j = 0; j < num_kv_blocks; ++j) {
           const int kv0 = j * kBlockKV;
@@ -241,12 +254,12 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             if (!ok) break;
             const uint32_t dst = s_k + s * TR::kGroupBytes, fb = bar(TR::kBarKFull + s);
             mbar_arrive_expect_tx(fb, TR::kGroupBytes);
-            tma_load_4d(dst, &p.k_main, fb, 0, kv0, h, b);
-            if constexpr (TAIL > 0) tma_load_4d(dst + TR::kMainBytes, &p.k_tail, fb, 64, kv0, h, b);
+            tma_load_4d(dst, &p.k_main, fb, xqk, kv0, h, b);
+            if constexpr (TAIL > 0) tma_load_4d(dst + TR::kMainBytes, &p.k_tail, fb, 64 + xqk, kv0, h, b);
             if constexpr (kDual) {
-              tma_load_4d(dst + TR::kTileBytes, &p.tk_main, fb, 0, kv0, h, b);
+              tma_load_4d(dst + TR::kTileBytes, &p.tk_main, fb, xqk, kv0, h, b);
               if constexpr (TAIL > 0)
-                tma_load_4d(dst + TR::kTileBytes + TR::kMainBytes, &p.tk_tail, fb, 64, kv0, h, b);
+                tma_load_4d(dst + TR::kTileBytes + TR::kMainBytes, &p.tk_tail, fb, 64 + xqk, kv0, h, b);
             }
             ++kcnt;
           }
@@ -259,9 +272,9 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             mbar_arrive_expect_tx(fb, TR::kVGroupBytes);
 #pragma unroll
             for (int a = 0; a < TR::kVAtoms; ++a) {
-              tma_load_4d(dst + a * TR::kVAtomBytes, &p.v_map, fb, a * 32, kv0, h, b);
+              tma_load_4d(dst + a * TR::kVAtomBytes, &p.v_map, fb, a * 32 + xv, kv0, h, b);
               if constexpr (kDual)
-                tma_load_4d(dst + TR::kVTileBytes + a * TR::kVAtomBytes, &p.tv_map, fb, a * 32, kv0, h, b);
+                tma_load_4d(dst + TR::kVTileBytes + a * TR::kVAtomBytes, &p.tv_map, fb, a * 32 + xv, kv0, h, b);
             }
             ++vcnt;
           }
@@ -615,6 +628,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       const float mu_tot = mu + xsum[256 + (1 - grp) * 128 + row];
       const float inv_l = 1.f / l_tot;
       const float mu_n = mu_tot * inv_l;
+      const int vshift = column_shift(p, 1, b, h);  // V columns (hence O / T columns) were loaded 8 early
       const int64_t lq = q0 + row;
       T* o_row = reinterpret_cast<T*>(p.o) + b * p.o_sb + lq * p.o_sl + h * p.o_sh;
       T* to_row = kDual ? reinterpret_cast<T*>(p.to) + b * p.to_sb + lq * p.to_sl + h * p.to_sh : nullptr;
@@ -639,8 +653,8 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         }
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          const int cc = c * 16 + hh * 8;
-          if (cc < p.head_dim) {
+          const int cc = c * 16 + hh * 8 - vshift;  // accumulator column -> head-dim column
+          if (cc >= 0 && cc < p.head_dim) {
             *reinterpret_cast<uint4*>(o_row + cc) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
             if constexpr (kDual)
               *reinterpret_cast<uint4*>(to_row + cc) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);

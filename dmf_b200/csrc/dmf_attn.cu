@@ -217,6 +217,31 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
   p.num_tiles = B * H * p.num_q_tiles;
   p.scale = a->softmax_scale;
   p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
+  if (D == 72) {
+    // head rows of 144 bytes straddle 32-byte sectors on every other head: let the kernel start its
+    // boxes 8 columns early there.  All tensors of a group must agree on the alignment pattern.
+    auto pattern = [](const dmf_attn_tensor& t, int* out) -> bool {
+      if ((t.stride_l * 2) % 32 != 0) return false;  // alignment must not change along the sequence
+      out[0] = static_cast<int>(reinterpret_cast<uintptr_t>(t.ptr) & 31);
+      out[1] = static_cast<int>((t.stride_b * 2) & 31);
+      out[2] = static_cast<int>((t.stride_h * 2) & 31);
+      return true;
+    };
+    const dmf_attn_tensor* g0[4] = {&a->q, &a->k, &a->tq, &a->tk};
+    const dmf_attn_tensor* g1[2] = {&a->v, &a->tv};
+    const dmf_attn_tensor* const* groups[2] = {g0, g1};
+    const int counts[2] = {dual ? 4 : 2, dual ? 2 : 1};
+    for (int g = 0; g < 2; ++g) {
+      int ref[3] = {0, 0, 0};
+      bool ok = pattern(*groups[g][0], ref);
+      for (int i = 1; ok && i < counts[g]; ++i) {
+        int cur[3];
+        ok = pattern(*groups[g][i], cur) && cur[0] == ref[0] && cur[1] == ref[1] && cur[2] == ref[2];
+      }
+      p.align_enable[g] = ok ? 1 : 0;
+      p.align0[g] = ref[0]; p.align_b[g] = ref[1]; p.align_h[g] = ref[2];
+    }
+  }
   const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   if (dt == DMF_ATTN_BF16)
