@@ -212,8 +212,20 @@ def run_ours(args):
     del qkv, tqkv
     ins = (q, k, v, tq, tk, tv)
 
+    # --op selects the entry point: the fused forward+tangent (the bench line), the plain forward, or the
+    # primal backward (both launches); flops and bytes follow the op
+    op = args.op
+    flop_factor = {"dual": 12.0, "fwd": 4.0, "bwd": 10.0}[op]
+    if op == "bwd":
+        o_saved, lse_saved = ops.fwd_raw(q, k, v, scale)
+        dout = torch.randn(B, L, H, D, device=dev, dtype=torch.float32, generator=gen).to(torch.bfloat16)
+
     def step():
-        return ops.fwd_dual_raw(*ins, scale)
+        if op == "dual":
+            return ops.fwd_dual_raw(*ins, scale)
+        if op == "fwd":
+            return ops.fwd_raw(q, k, v, scale)
+        return ops.bwd_raw(dout, q, k, v, o_saved, lse_saved, scale)
 
     def sync_all():
         if world > 1:
@@ -243,12 +255,12 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
-    fl = _flops(B, L, H, D)
+    fl = _flops(B, L, H, D) * flop_factor / 12.0
     value = world * fl / (ms_step * 1e-3) / 1e12
 
     # ---- end to end through the public API, host buffers, copies inside the timed region ----
     e2e_steps = max(1, min(args.steps, 10))
-    if args.no_e2e:
+    if args.no_e2e or op != "dual":
         e2e_steps = 0
     host_in = [x.contiguous().cpu().pin_memory() for x in ins]
     dev_in = [torch.empty_like(x, device=dev) for x in host_in]
@@ -286,19 +298,22 @@ def run_ours(args):
 
     peaks = _peaks()
     achieved = fl / (ms_step * 1e-3) / 1e12  # per launch, per GPU
+    # dual: read 6 tensors, write 2 (+ lse); fwd: read 3, write 1 (+ lse); bwd: read 5 (+ lse), write 3
+    algo_bytes = {"dual": 16.0, "fwd": 8.0, "bwd": 16.0}[op] * B * L * H * D + 4.0 * B * H * L
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
         "frac": achieved / peaks["tflops"], "traffic": _traffic(args.workload),
         "peak_source": f"bf16 burst, of {peaks['source']}",
         "frac_of_sustained": (achieved / peaks["tflops_sustained"]) if peaks["tflops_sustained"] else None,
         "frac_of_nominal_2250": achieved / 2250.0,
-        "algorithmic_flops_per_launch": fl, "algorithmic_bytes_per_launch": _algo_bytes(B, L, H, D),
-        "hbm_gbs_achieved": _algo_bytes(B, L, H, D) / (ms_step * 1e-3) / 1e9,
-        "kernel": "attn_fwd_kernel<bf16, TAIL=16, dual>",
+        "algorithmic_flops_per_launch": fl, "algorithmic_bytes_per_launch": algo_bytes,
+        "hbm_gbs_achieved": algo_bytes / (ms_step * 1e-3) / 1e9,
+        "kernel": {"dual": "attn_fwd_kernel<bf16, TAIL=16, dual>", "fwd": "attn_fwd_kernel<bf16, TAIL=16, plain>",
+                   "bwd": "attn_bwd_kernel<bf16, TAIL=16, dQ> + attn_bwd_kernel<bf16, TAIL=16, dK/dV>"}[op],
     }
 
     cpu_base = None
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and op == "dual":
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
         cstep, cfl = _cpu_step_fn(args.workload, CPU_SAMPLE_BATCH)
@@ -312,7 +327,8 @@ def run_ours(args):
         }
 
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if op == "dual" else f"attn_{op}_tflops", "value": value, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {desc}", "per_gpu_batch": B,
@@ -320,11 +336,12 @@ def run_ours(args):
                    "layout": "q,k contiguous after qk-norm; v and tangents strided views of packed qkv"
                              if qkn else "strided views of packed qkv"},
         "roofline": roofline,
+        "op": op,
         "cpu_baseline": cpu_base,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps, "ms_per_step": (e2e_ms / e2e_steps) if e2e_steps else None,
                 "api": "torch.func.jvp(dmf_b200.flash_attn_func) on pinned host tensors"},
-        "gpu_launches": args.steps,
+        "gpu_launches": args.steps * (2 if op == "bwd" else 1),
         "clocks": sampler.summary(),
     }
     print(json.dumps(line), flush=True)
@@ -461,6 +478,8 @@ def main():
                          "global batch 256; C5: DMFT-XL/2 4-step Euler sampling at 512px, 64 images per GPU")
     ap.add_argument("--micro-batch", type=int, default=32, help="C4: images per forward/backward pass")
     ap.add_argument("--model", default="DMFT-XL/2", help="C4/C5: harness model name (smaller ones for smoke runs)")
+    ap.add_argument("--op", choices=["dual", "fwd", "bwd"], default="dual",
+                    help="C2/C3: entry point to time (default: the fused forward+tangent, which is the bench line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=None,
