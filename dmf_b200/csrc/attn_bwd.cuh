@@ -80,17 +80,6 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src,
                : "memory");
 }
 
-template <typename T>
-__device__ __forceinline__ float2 unpack2(uint32_t u);
-template <>
-__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
-  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
-}
-template <>
-__device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
-  return __half22float2(*reinterpret_cast<__half2*>(&u));
-}
-
 template <typename T, int TAIL, int kMode>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ BwdParams p) {

@@ -113,6 +113,9 @@ struct FwdTraits {
   // next block can be issued as soon as the softmax has read the current S, instead of behind the
   // P V products that read P.  Otherwise P is written over S.
   static constexpr bool kSepP = kDual && (kDPad <= 96);
+  // With P in its own columns the two softmax warpgroups split by role instead of by column:
+  // one turns S into P (all 128 columns of its row), the other turns dS and P into G.
+  static constexpr bool kRoleSplit = kSepP;
   static constexpr uint32_t kColS = 0, kColDS = 128, kColP = 256, kColO = kSepP ? 320 : 256,
                             kColT = kColO + kDPad;
   static constexpr uint32_t kTmemCols = 512;
@@ -205,9 +208,14 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < TR::kNumBars; ++i) {
-      const bool softmax_arrives =
-          (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarXchg || i == TR::kBarSEmpty);
-      mbar_init(bar(i), softmax_arrives ? static_cast<uint32_t>(kSoftmaxWarps) : 1u);  // one arrival per warp
+      // arrivals: softmax warps arrive once per warp; tcgen05.commit and the TMA producer arrive once
+      uint32_t count = 1;
+      if (i == TR::kBarXchg) count = kSoftmaxWarps;
+      if (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarSEmpty)
+        count = TR::kRoleSplit ? kSoftmaxWarps / 2 : kSoftmaxWarps;
+      if (i == TR::kBarPEmpty && TR::kRoleSplit) count = 1 + kSoftmaxWarps / 2;  // commit + the G warps
+      if (!kDual && i == TR::kBarGFull) count = kSoftmaxWarps;  // plain pass: second "P ready" barrier
+      mbar_init(bar(i), count);
     }
     fence_mbar_init();
   }
@@ -372,7 +380,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             if (!ok) break;
             ++gcnt;
             tc_fence_after_sync();
-            issue_pv_atoms<TR, true>(leader, t_t, t_ds, vt, idesc_pv, true);  // T += G V
+            issue_pv_atoms<TR, !TR::kRoleSplit>(leader, t_t, t_ds, vt, idesc_pv, true);  // T += G V
             commit(TR::kBarAccFull);
             commit(TR::kBarVEmpty + sv);
             ++vcnt;
@@ -427,6 +435,219 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     }
   } else {
     // ===================== softmax / correction / epilogue ==================
+    if constexpr (TR::kRoleSplit) {
+      // Role split (dual pass, P in its own tensor-memory columns).  Both warpgroups map thread ->
+      // query row (lane quarter = warp % 4).  Warps 2-5 ("P warps") turn S into P: row max, lazy
+      // rescale of the accumulators, exp2, row sum l.  Warps 6-9 ("G warps") turn dS and the
+      // 16-bit P into G = P * dS * scale and keep mu = rowsum(G).  They meet once per tile, in the
+      // epilogue, to combine l and mu.  No per-block exchange, and the two halves of the softmax
+      // work run concurrently instead of one after the other.
+      const bool p_role = warp < 6;
+      const int quarter = warp & 3;
+      const int row = quarter * 32 + lane;
+      const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+      const uint32_t t_s = tmem + lane_base + TR::kColS, t_ds = tmem + lane_base + TR::kColDS;
+      const uint32_t t_p = tmem + lane_base + TR::kColP, t_o = tmem + lane_base + TR::kColO;
+      const float sl2 = p.scale_log2e;
+      float* xalpha = xchg;        // [block parity][row]: factor the P warps applied to the accumulators
+      float* xsum = xchg + 256;    // [l | mu][row]
+      uint32_t gblk = 0, xuse = 0;
+      bool ok = true;
+      auto wait = [&](int b_, uint32_t parity) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleSoftmax + b_));
+      };
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        const int bh = tile / p.num_q_tiles;
+        const int q0 = (tile % p.num_q_tiles) * kBlockQ;
+        const int b = bh / p.heads, h = bh % p.heads;
+        float m_used = -CUDART_INF_F, l = 0.f, mu = 0.f;
+        for (int j = 0; j < num_kv_blocks; ++j, ++gblk) {
+          if (p_role) {
+            // ---- S -> P ------------------------------------------------------
+            ok = wait(TR::kBarSFull, gblk & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t r[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, r[c]);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive_warp(bar(TR::kBarSEmpty));  // S is in registers: the next S may be computed
+            float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                mx0 = max3(mx0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                mx1 = max3(mx1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+                mx2 = max3(mx2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+                mx3 = max3(mx3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
+              }
+            }
+            const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+            float alpha = 1.f;
+            if (j == 0) {
+              m_used = m_blk;
+            } else {
+              const bool need = m_blk > m_used + kRescaleThreshold;
+              if (__any_sync(0xffffffffu, need)) {
+                // every MMA that accumulated into O / T for the previous blocks must be done: the
+                // commit of block g-2 is complete (S of this block was issued after it), so the
+                // barrier is at most one phase ahead
+                ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (need) {
+                  alpha = fast_exp2(m_used - m_blk);
+                  m_used = m_blk;
+                }
+                l *= alpha;
+#pragma unroll 1
+                for (int c = 0; c < 2 * DPAD / 16; ++c) {
+                  uint32_t a[16];
+                  tmem_ld_x16(t_o + c * 16, a);
+                  tmem_wait_ld();
+#pragma unroll
+                  for (int i = 0; i < 16; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) * alpha);
+                  tmem_st_x16(t_o + c * 16, a);
+                }
+                tmem_wait_st();
+              }
+            }
+            xalpha[(gblk & 1u) * 128 + row] = alpha;  // the G warps scale mu by the same factor
+            const uint64_t sl2_2 = pack_f2(sl2, sl2), neg_m2 = pack_f2(-m_used, -m_used);
+            uint64_t la = pack_f2(0.f, 0.f), lb = la;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                // of every four elements two go through the MUFU unit and two through the FMA-pipe cubic
+                float x0, x1, p2, p3;
+                unpack_f2(fma2(pack_u2(r[c][i], r[c][i + 1]), sl2_2, neg_m2), x0, x1);
+                poly_exp2_x2(fma2(pack_u2(r[c][i + 2], r[c][i + 3]), sl2_2, neg_m2), p2, p3);
+                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                la = add2(la, pack_f2(p0, p1));
+                lb = add2(lb, pack_f2(p2, p3));
+                r[c][i / 2] = Pack2<T>::pack(p0, p1);       // packed in place: word k holds elements 2k, 2k+1
+                r[c][i / 2 + 1] = Pack2<T>::pack(p2, p3);
+              }
+            }
+            {
+              float s0, s1;
+              unpack_f2(add2(la, lb), s0, s1);
+              l += s0 + s1;
+            }
+            if (gblk > 0) {  // the P V products of the previous block and the G warps have read P
+              ok = wait(TR::kBarPEmpty, (gblk - 1u) & 1u);
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pk[i] = r[c][i];
+              tmem_st_x16(t_p + c * 16, pk);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive_warp(bar(TR::kBarPFull));
+          } else {
+            // ---- G = P * dS * scale, mu += rowsum(G) ---------------------------
+            ok = wait(TR::kBarDSFull, gblk & 1u);
+            if (!ok) break;
+            ok = wait(TR::kBarPFull, gblk & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            mu *= xalpha[(gblk & 1u) * 128 + row];
+            const uint64_t scale2 = pack_f2(p.scale, p.scale);
+            uint64_t mua = pack_f2(0.f, 0.f), mub = mua;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t d[32], pp[16];
+              tmem_ld_x32(t_ds + c * 32, d);
+              tmem_ld_x16(t_p + c * 16, pp);
+              tmem_wait_ld();
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; i += 2) {
+                const float2 pa = unpack2<T>(pp[i]), pb = unpack2<T>(pp[i + 1]);
+                const uint64_t ga = mul2(pack_f2(pa.x, pa.y), mul2(pack_u2(d[2 * i], d[2 * i + 1]), scale2));
+                const uint64_t gb = mul2(pack_f2(pb.x, pb.y), mul2(pack_u2(d[2 * i + 2], d[2 * i + 3]), scale2));
+                mua = add2(mua, ga);
+                mub = add2(mub, gb);
+                float g0, g1, g2, g3;
+                unpack_f2(ga, g0, g1);
+                unpack_f2(gb, g2, g3);
+                pk[i] = Pack2<T>::pack(g0, g1);
+                pk[i + 1] = Pack2<T>::pack(g2, g3);
+              }
+              tmem_st_x16(t_ds + c * 16, pk);  // over dS columns this thread has already read
+            }
+            {
+              float s0, s1;
+              unpack_f2(add2(mua, mub), s0, s1);
+              mu += s0 + s1;
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive_warp(bar(TR::kBarPEmpty));  // P has been read
+            mbar_arrive_warp(bar(TR::kBarGFull));
+          }
+        }
+        if (!ok) break;
+        // ---- epilogue: combine l and mu, normalise, write o, to, lse --------------
+        // The meeting comes first: a G warp only gets here after it has seen dS of the last block,
+        // which was issued after the G V product of the block before, so once everybody has met the
+        // accumulator barrier is at most one phase ahead of any waiter.
+        xsum[(p_role ? 0 : 128) + row] = p_role ? l : mu;
+        mbar_arrive_warp(bar(TR::kBarXchg));
+        ok = wait(TR::kBarXchg, xuse & 1u);
+        ++xuse;
+        if (!ok) break;
+        ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const float l_tot = xsum[row], mu_tot = xsum[128 + row];
+        const float inv_l = 1.f / l_tot;
+        const float mu_n = mu_tot * inv_l;
+        const int vshift = column_shift(p, 1, b, h);
+        const int64_t lq = q0 + row;
+        T* o_row = reinterpret_cast<T*>(p.o) + b * p.o_sb + lq * p.o_sl + h * p.o_sh;
+        T* to_row = reinterpret_cast<T*>(p.to) + b * p.to_sb + lq * p.to_sl + h * p.to_sh;
+#pragma unroll
+        for (int c = 0; c < DPAD / 16; ++c) {
+          if ((c & 1) != (p_role ? 0 : 1)) continue;  // the two groups alternate 16-column chunks
+          uint32_t a[16], t[16];
+          tmem_ld_x16(t_o + c * 16, a);
+          tmem_ld_x16(t_o + DPAD + c * 16, t);
+          tmem_wait_ld();
+          uint32_t po[8], pt[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float o0 = __uint_as_float(a[2 * i]) * inv_l;
+            const float o1 = __uint_as_float(a[2 * i + 1]) * inv_l;
+            po[i] = Pack2<T>::pack(o0, o1);
+            const float t0 = fmaf(__uint_as_float(t[2 * i]), inv_l, -mu_n * o0);
+            const float t1 = fmaf(__uint_as_float(t[2 * i + 1]), inv_l, -mu_n * o1);
+            pt[i] = Pack2<T>::pack(t0, t1);
+          }
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int cc = c * 16 + hh * 8 - vshift;
+            if (cc >= 0 && cc < p.head_dim) {
+              *reinterpret_cast<uint4*>(o_row + cc) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
+              *reinterpret_cast<uint4*>(to_row + cc) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
+            }
+          }
+        }
+        if (p_role)
+          p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seqlen_q + lq] =
+              (m_used + __log2f(l_tot)) * 0.6931471805599453f;
+        tc_fence_before_sync();
+      }
+    } else {
+    // Column split (plain forward, and the dual pass when P has to share columns with S).
     // Two warpgroups (warps 2-5 and 6-9).  A thread owns one query row (tensor-memory lane
     // = 32 * (warp % 4) + lane) and one half of the 128 score columns: group g reads S / dS
     // columns [64g, 64g+64) and writes its 16-bit P / G back over the first 32 of those columns
@@ -667,6 +888,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       // the accumulator reads above must be complete before the next tile's first MMA overwrites O / T
       tc_fence_before_sync();
     }
+    }  // column split
   }
 
   // ============================== teardown ==================================

@@ -333,6 +333,31 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// 2^x for a pair of fp32 values on the FMA / ALU pipes (no MUFU): round x to the nearest integer
+// n with the 1.5 * 2^23 trick, evaluate a cubic for 2^(x - n) on [-0.5, 0.5] (max relative error
+// 7.5e-5, far below the rounding of a 16-bit P) and add n into the exponent field.  The MUFU unit
+// delivers 16 exp2 per clock per SM, which for a 128 x 128 score block is half of the tensor-pipe
+// time of the block; doing part of the exponentials here takes it off the critical path.
+__device__ __forceinline__ void poly_exp2_x2(uint64_t x2, float& e0, float& e1) {
+  float x0, x1;
+  unpack_f2(x2, x0, x1);
+  x0 = fmaxf(x0, -125.f);  // below this the result is < 2^-125: flush instead of wrapping the exponent
+  x1 = fmaxf(x1, -125.f);
+  const uint64_t xc = pack_f2(x0, x1);
+  const uint64_t magic = pack_f2(12582912.f, 12582912.f);
+  const uint64_t t = add2(xc, magic);                                   // low mantissa bits = n
+  const uint64_t n = add2(t, pack_f2(-12582912.f, -12582912.f));        // n as a float
+  const uint64_t r = fma2(n, pack_f2(-1.f, -1.f), xc);                  // x - n
+  uint64_t q = fma2(r, pack_f2(0.0551716648f, 0.0551716648f), pack_f2(0.2426111251f, 0.2426111251f));
+  q = fma2(q, r, pack_f2(0.6932609677f, 0.6932609677f));
+  q = fma2(q, r, pack_f2(0.9999280572f, 0.9999280572f));
+  float q0, q1, t0, t1;
+  unpack_f2(q, q0, q1);
+  unpack_f2(t, t0, t1);
+  e0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  e1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 template <typename T>
 struct Pack2;
 template <>
@@ -351,5 +376,17 @@ struct Pack2<__half> {
     return *reinterpret_cast<uint32_t*>(&v);
   }
 };
+
+// two 16-bit floats -> fp32
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t u);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
+  return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
 
 }  // namespace dmf

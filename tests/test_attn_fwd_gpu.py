@@ -18,7 +18,7 @@ DEV = "cuda:0"
 
 TOL_SAME_INPUTS = 6e-3
 TOL_BAR = 2e-2
-TOL_LSE = 2e-5
+TOL_LSE = 1e-4   # half of the exponentials use a cubic with 7.5e-5 relative error, which moves ln(l) by up to that much
 
 
 def _inputs(B, L, H, D, *, seed=0, ts=0.5, dtype=torch.bfloat16, qk_norm=False):
