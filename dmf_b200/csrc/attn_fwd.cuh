@@ -45,7 +45,13 @@ constexpr int kBlockQ = 128;
 constexpr int kBlockKV = 128;
 constexpr int kFwdThreads = 320;       // TMA warp, MMA warp, two softmax warpgroups
 constexpr int kSoftmaxWarps = 8;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8
+constexpr float kRescaleThreshold = 8.0f;
+// Of every kPolyEvery groups of four score elements, one group computes two of its four exp2 on
+// the FMA pipe (cubic) instead of the MUFU unit: 1 -> half of all exp2, 2 -> a quarter, 0 -> none.
+#ifndef DMF_POLY_EVERY
+#define DMF_POLY_EVERY 2
+#endif
+constexpr int kPolyEvery = DMF_POLY_EVERY;  // log2 units: P stays below 2^8
 
 // Codes written to the status word when a wait gives up: role * 100 + barrier.
 constexpr int kRoleProducer = 100, kRoleMma = 200, kRoleSoftmax = 300;
@@ -521,10 +527,17 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             for (int c = 0; c < 4; ++c) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
-                // of every four elements two go through the MUFU unit and two through the FMA-pipe cubic
                 float x0, x1, p2, p3;
                 unpack_f2(fma2(pack_u2(r[c][i], r[c][i + 1]), sl2_2, neg_m2), x0, x1);
-                poly_exp2_x2(fma2(pack_u2(r[c][i + 2], r[c][i + 3]), sl2_2, neg_m2), p2, p3);
+                const uint64_t xb = fma2(pack_u2(r[c][i + 2], r[c][i + 3]), sl2_2, neg_m2);
+                if (kPolyEvery > 0 && ((i / 4) % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery - 1)) {
+                  poly_exp2_x2(xb, p2, p3);  // FMA-pipe cubic
+                } else {
+                  float x2, x3;
+                  unpack_f2(xb, x2, x3);
+                  p2 = fast_exp2(x2);
+                  p3 = fast_exp2(x3);
+                }
                 const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                 la = add2(la, pack_f2(p0, p1));
                 lb = add2(lb, pack_f2(p2, p3));
