@@ -1,0 +1,534 @@
+// Fused forward + tangent attention for sm_100a, CTA-pair variant.
+//
+// Same algorithm, roles and tensor-memory layout as the dual pass of attn_fwd.cuh (P warps, G warps,
+// one MMA-issuing warp, one TMA warp), but two CTAs of a cluster work on two neighbouring 128-row
+// query tiles of the same (batch, head) and run every MMA together as one tcgen05.mma of M = 256
+// with .cta_group::2:
+//
+//   * each CTA keeps its own query tile (A operand) and its own S / dS / P / O / T in tensor memory;
+//   * the B operand is split between the two CTAs, so each CTA loads only HALF of every K/dK block
+//     (64 of the 128 key rows) and HALF of every V/dV block (DPAD/2 of the head-dim columns).
+//
+// That halves the L2 -> shared-memory traffic per query tile (the single-CTA kernel re-reads all of
+// K/dK/V/dV of a head for each of its query tiles) and the shared-memory footprint of the rings,
+// which pays for a third ring stage.  Loads are plain per-CTA TMA loads (no cluster multicast); only
+// tcgen05.commit fans its barrier arrival out to both CTAs.
+//
+// Barrier placement: "operand ready" barriers that the MMA warp waits on live in the LEADER CTA
+// (rank 0) and are arrived on by both CTAs (TMA transaction bytes, softmax warps); barriers that
+// a CTA's own warps wait on (S ready, dS ready, ring slot free, accumulators done ...) are local and
+// are arrived on by the leader's tcgen05.commit with a two-CTA multicast mask.
+//
+// V column order.  CTA r holds DPAD/2 columns of V: columns [32r, 32r+32) and, when DPAD > 64, the
+// e = DPAD/2 - 32 columns [64 + r e, 64 + r e + e).  Accumulator column t therefore maps to head-dim
+// column   t            for t in [0, 32)
+//          64 + t - 32  for t in [32, 32+e)
+//          32 + t - h   for t in [h, h+32)        (h = DPAD/2)
+//          64 + e + t - h - 32   for t in [h+32, DPAD)
+// and the epilogue stores accordingly.
+#pragma once
+
+#include "attn_fwd.cuh"
+
+namespace dmf {
+
+template <int TAIL>
+struct PairTraits {
+  static_assert(TAIL == 0 || TAIL == 16 || TAIL == 32, "the pair kernel needs P in its own tensor-memory columns");
+  static constexpr int kDPad = 64 + TAIL;
+  static constexpr int kHalf = kDPad / 2;           // V / O columns per CTA
+  static constexpr int kExtra = kHalf - 32;         // columns of the second V atom that are used
+  // query tile (A operand), 128 rows
+  static constexpr int kMainBytes = 128 * 128;
+  static constexpr int kTailBytes = 128 * TAIL * 2;
+  static constexpr int kTileBytes = kMainBytes + kTailBytes;
+  static constexpr int kQGroupBytes = 2 * kTileBytes;
+  // this CTA's half of a K / dK block, 64 rows
+  static constexpr int kKMainBytes = 64 * 128;
+  static constexpr int kKTailBytes = 64 * TAIL * 2;
+  static constexpr int kKTileBytes = kKMainBytes + kKTailBytes;
+  static constexpr int kKGroupBytes = 2 * kKTileBytes;
+  // this CTA's half of a V / dV block: atoms of 32 columns x 128 rows, 64-byte swizzle
+  static constexpr int kVAtoms = kExtra > 0 ? 2 : 1;
+  static constexpr int kVAtomBytes = 128 * 64;
+  static constexpr int kVTileBytes = kVAtoms * kVAtomBytes;
+  static constexpr int kVGroupBytes = 2 * kVTileBytes;
+  static constexpr int kStagesK = 3, kStagesV = 3;
+  static constexpr int kTileSmem = kQGroupBytes + kStagesK * kKGroupBytes + kStagesV * kVGroupBytes;
+  static constexpr int kXchgBytes = 2048;
+  // barriers
+  static constexpr int kBarQFull = 0, kBarQEmpty = 1, kBarSFull = 2, kBarDSFull = 3, kBarPFull = 4, kBarGFull = 5,
+                       kBarAccFull = 6, kBarXchg = 7, kBarSEmpty = 8, kBarPEmpty = 9, kBarPG = 10, kBarKFull = 11,
+                       kBarKEmpty = kBarKFull + kStagesK, kBarVFull = kBarKEmpty + kStagesK,
+                       kBarVEmpty = kBarVFull + kStagesV, kNumBars = kBarVEmpty + kStagesV;
+  static constexpr int kSmemBytes = 1024 + kTileSmem + kXchgBytes + kNumBars * 8 + 16;
+  // tensor memory columns (per CTA)
+  static constexpr uint32_t kColS = 0, kColDS = 128, kColP = 256, kColO = 320, kColT = 320 + kDPad;
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kTailSwizzle = TAIL == 32 ? kSwizzle64 : kSwizzle32;
+  static constexpr uint32_t kTailRowBytes = 2 * TAIL;
+};
+
+constexpr int kPairThreads = 320;
+
+// head-dim column of accumulator column t (t a multiple of 8); see the header comment
+template <typename TR>
+__device__ __forceinline__ int pair_head_col(int t) {
+  constexpr int h = TR::kHalf, e = TR::kExtra;
+  if (t < 32) return t;
+  if (t < h) return 64 + (t - 32);
+  if (t < h + 32) return 32 + (t - h);
+  return 64 + e + (t - h - 32);
+}
+
+// acc[256 x 128] (+)= A[256 x D] * B[128 x D]^T: each CTA's A tile has 128 rows, each CTA's B tile 64 rows
+template <int TAIL, typename TR>
+__device__ __forceinline__ void issue_qk_pair(bool leader, uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile,
+                                              uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+    const uint64_t ad = make_smem_desc(a_tile + kk * 32, 16, 1024, kSwizzle128);
+    const uint64_t bd = make_smem_desc(b_tile + kk * 32, 16, 1024, kSwizzle128);
+    mma_ss_pair(d_tmem, ad, bd, idesc, (accumulate || kk > 0) ? 1u : 0u, leader);
+  }
+#pragma unroll
+  for (int kk = 0; kk < TAIL / 16; ++kk) {
+    const uint64_t ad = make_smem_desc(a_tile + TR::kMainBytes + kk * 32, 16, 8 * TR::kTailRowBytes, TR::kTailSwizzle);
+    const uint64_t bd = make_smem_desc(b_tile + TR::kKMainBytes + kk * 32, 16, 8 * TR::kTailRowBytes, TR::kTailSwizzle);
+    mma_ss_pair(d_tmem, ad, bd, idesc, 1u, leader);
+  }
+}
+
+// acc[256 x DPAD] (+)= A[256 x 128] * V[128 x DPAD]; A from each CTA's tensor memory, each CTA's V tile
+// holds DPAD/2 columns as 64-byte-swizzled atoms of 32 columns
+template <typename TR>
+__device__ __forceinline__ void issue_pv_pair(bool leader, uint32_t d_tmem, uint32_t a_tmem, uint32_t v_tile,
+                                              uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < kBlockKV / 16; ++kk) {
+    const uint64_t bd = make_smem_desc(v_tile + kk * (16 * 64), TR::kVAtomBytes, 8 * 64, kSwizzle64);
+    mma_ts_pair(d_tmem, a_tmem + kk * 8, bd, idesc, (accumulate || kk > 0) ? 1u : 0u, leader);
+  }
+}
+
+// ---- the kernel ---------------------------------------------------------------
+// p.k_* maps have a box of 64 rows; p.num_tiles counts tile PAIRS; p.num_q_tiles is even.
+
+template <typename T, int TAIL>
+__global__ void __launch_bounds__(kPairThreads, 1)
+attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
+  using TR = PairTraits<TAIL>;
+  constexpr int DPAD = TR::kDPad;
+  constexpr bool kBf16 = Pack2<T>::kIsBf16;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t s_q = smem_u32(smem);
+  const uint32_t s_k = s_q + TR::kQGroupBytes;
+  const uint32_t s_v = s_k + TR::kStagesK * TR::kKGroupBytes;
+  float* xchg = reinterpret_cast<float*>(smem + TR::kTileSmem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TR::kTileSmem + TR::kXchgBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + TR::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) -> uint32_t { return bar0 + 8u * static_cast<uint32_t>(i); };       // this CTA's barrier
+  auto lbar = [&](int i) -> uint32_t { return map_to_cta(bar(i), 0); };                      // the leader's barrier
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int num_kv_blocks = p.seqlen_kv / kBlockKV;
+  const int pairs_per_bh = p.num_q_tiles >> 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < TR::kNumBars; ++i) {
+      uint32_t count = 1;  // tcgen05.commit (multicast from the leader)
+      if (i == TR::kBarQFull || (i >= TR::kBarKFull && i < TR::kBarKEmpty) || (i >= TR::kBarVFull && i < TR::kBarVEmpty))
+        count = 2;  // one producer arrival (+ its transaction bytes) per CTA
+      if (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarSEmpty) count = 8;  // 4 warps of each CTA
+      if (i == TR::kBarXchg) count = 8;    // the 8 local softmax warps
+      if (i == TR::kBarPG) count = 4;      // the 4 local P warps
+      if (i == TR::kBarPEmpty) count = 5;  // commit + the 4 local G warps
+      mbar_init(bar(i), count);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc_pair(smem_u32(tmem_slot), TR::kTmemCols);
+    tmem_relinquish_alloc_permit_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anybody arrives remotely
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // =========================== TMA producer (each CTA) ====================
+    if (lane == 0) {
+      prefetch_tensor_map(&p.q_main);
+      prefetch_tensor_map(&p.k_main);
+      prefetch_tensor_map(&p.v_map);
+      uint32_t kcnt = 0, vcnt = 0, tcnt = 0;
+      bool ok = true;
+      auto wait = [&](int b_, uint32_t parity) -> bool {
+        return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleProducer + b_);
+      };
+      for (int pp = cluster_id; ok && pp < p.num_tiles; pp += num_clusters, ++tcnt) {
+        const int bh = pp / pairs_per_bh;
+        const int q0 = (2 * (pp % pairs_per_bh) + static_cast<int>(rank)) * kBlockQ;
+        const int b = bh / p.heads, h = bh % p.heads;
+        const int xqk = -column_shift(p, 0, b, h);
+        ok = wait(TR::kBarQEmpty, (tcnt & 1u) ^ 1u);
+        if (!ok) break;
+        const uint32_t qf = lbar(TR::kBarQFull);
+        mbar_arrive_expect_tx_cluster(qf, TR::kQGroupBytes);
+        tma_load_4d_pair(s_q, &p.q_main, qf, xqk, q0, h, b);
+        tma_load_4d_pair(s_q + TR::kTileBytes, &p.tq_main, qf, xqk, q0, h, b);
+        if constexpr (TAIL > 0) {
+          tma_load_4d_pair(s_q + TR::kMainBytes, &p.q_tail, qf, 64 + xqk, q0, h, b);
+          tma_load_4d_pair(s_q + TR::kTileBytes + TR::kMainBytes, &p.tq_tail, qf, 64 + xqk, q0, h, b);
+        }
+        for (int j = 0; j < num_kv_blocks; ++j) {
+          const int kv0 = j * kBlockKV;
+          {
+            const uint32_t s = kcnt % TR::kStagesK, ph = (kcnt / TR::kStagesK) & 1u;
+            ok = wait(TR::kBarKEmpty + s, ph ^ 1u);
+            if (!ok) break;
+            const uint32_t dst = s_k + s * TR::kKGroupBytes, fb = lbar(TR::kBarKFull + s);
+            const int kr = kv0 + 64 * static_cast<int>(rank);  // this CTA's half of the key rows
+            mbar_arrive_expect_tx_cluster(fb, TR::kKGroupBytes);
+            tma_load_4d_pair(dst, &p.k_main, fb, xqk, kr, h, b);
+            tma_load_4d_pair(dst + TR::kKTileBytes, &p.tk_main, fb, xqk, kr, h, b);
+            if constexpr (TAIL > 0) {
+              tma_load_4d_pair(dst + TR::kKMainBytes, &p.k_tail, fb, 64 + xqk, kr, h, b);
+              tma_load_4d_pair(dst + TR::kKTileBytes + TR::kKMainBytes, &p.tk_tail, fb, 64 + xqk, kr, h, b);
+            }
+            ++kcnt;
+          }
+          {
+            const uint32_t s = vcnt % TR::kStagesV, ph = (vcnt / TR::kStagesV) & 1u;
+            ok = wait(TR::kBarVEmpty + s, ph ^ 1u);
+            if (!ok) break;
+            const uint32_t dst = s_v + s * TR::kVGroupBytes, fb = lbar(TR::kBarVFull + s);
+            mbar_arrive_expect_tx_cluster(fb, TR::kVGroupBytes);
+            const int x0 = 32 * static_cast<int>(rank);                   // columns [32r, 32r+32)
+            tma_load_4d_pair(dst, &p.v_map, fb, x0, kv0, h, b);
+            tma_load_4d_pair(dst + TR::kVTileBytes, &p.tv_map, fb, x0, kv0, h, b);
+            if constexpr (TR::kVAtoms > 1) {
+              const int x1 = 64 + TR::kExtra * static_cast<int>(rank);    // columns [64 + r e, ...): e of them used
+              tma_load_4d_pair(dst + TR::kVAtomBytes, &p.v_map, fb, x1, kv0, h, b);
+              tma_load_4d_pair(dst + TR::kVTileBytes + TR::kVAtomBytes, &p.tv_map, fb, x1, kv0, h, b);
+            }
+            ++vcnt;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer (leader CTA only) =======================
+    // Warp-uniform control flow; one elected lane issues.  Every MMA is a .cta_group::2 instruction
+    // that reads operands from, and writes accumulators to, both CTAs; every commit arrives on the
+    // same-named barrier of both CTAs.
+    if (rank == 0) {
+      const bool leader = elect_one();
+      auto commit = [&](int b_) { tc_commit_pair(bar(b_), leader); };
+      constexpr uint32_t idesc_qk = make_idesc(kBf16, false, false, 256, 128);
+      constexpr uint32_t idesc_pv = make_idesc(kBf16, false, true, 256, DPAD);
+      const uint32_t t_s = tmem + TR::kColS, t_ds = tmem + TR::kColDS, t_p = tmem + TR::kColP;
+      const uint32_t t_o = tmem + TR::kColO, t_t = tmem + TR::kColT;
+      uint32_t kcnt = 0, vcnt = 0, tcnt = 0, pcnt = 0, gcnt = 0, scnt = 0;
+      bool ok = true;
+      auto wait = [&](int b_, uint32_t parity) -> bool {
+        return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_);
+      };
+      for (int pp = cluster_id; ok && pp < p.num_tiles; pp += num_clusters, ++tcnt) {
+        ok = wait(TR::kBarQFull, tcnt & 1u);
+        if (!ok) break;
+        uint32_t sk = 0, kt = 0;
+        // S of the next block: needs the softmax of BOTH CTAs to have read the current S, and the K halves
+        auto issue_s = [&]() -> bool {
+          sk = kcnt % TR::kStagesK;
+          if (scnt > 0 && !wait(TR::kBarSEmpty, (scnt - 1u) & 1u)) return false;
+          if (!wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK) & 1u)) return false;
+          tc_fence_after_sync();
+          kt = s_k + sk * TR::kKGroupBytes;
+          issue_qk_pair<TAIL, TR>(leader, t_s, s_q, kt, idesc_qk, false);
+          commit(TR::kBarSFull);
+          ++scnt;
+          return true;
+        };
+        auto issue_ds = [&](bool last_of_tile) {
+          issue_qk_pair<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, kt, idesc_qk, false);
+          issue_qk_pair<TAIL, TR>(leader, t_ds, s_q, kt + TR::kKTileBytes, idesc_qk, true);
+          commit(TR::kBarDSFull);
+          commit(TR::kBarKEmpty + sk);
+          ++kcnt;
+          if (last_of_tile) commit(TR::kBarQEmpty);
+        };
+        ok = issue_s();
+        if (!ok) break;
+        issue_ds(num_kv_blocks == 1);
+        for (int j = 0; j < num_kv_blocks; ++j) {
+          const uint32_t sv = vcnt % TR::kStagesV;
+          const uint32_t vt = s_v + sv * TR::kVGroupBytes;
+          const bool more = (j + 1 < num_kv_blocks);
+          if (more) {
+            ok = issue_s();
+            if (!ok) break;
+          }
+          ok = wait(TR::kBarVFull + sv, (vcnt / TR::kStagesV) & 1u);
+          if (!ok) break;
+          ok = wait(TR::kBarPFull, pcnt & 1u);
+          if (!ok) break;
+          ++pcnt;
+          tc_fence_after_sync();
+          issue_pv_pair<TR>(leader, t_o, t_p, vt, idesc_pv, j > 0);                    // O += P V
+          issue_pv_pair<TR>(leader, t_t, t_p, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
+          commit(TR::kBarPEmpty);
+          ok = wait(TR::kBarGFull, gcnt & 1u);
+          if (!ok) break;
+          ++gcnt;
+          tc_fence_after_sync();
+          issue_pv_pair<TR>(leader, t_t, t_ds, vt, idesc_pv, true);                    // T += G V
+          commit(TR::kBarAccFull);
+          commit(TR::kBarVEmpty + sv);
+          ++vcnt;
+          if (more) issue_ds(j + 2 == num_kv_blocks);
+        }
+      }
+    }
+  } else {
+    // ===================== softmax / correction / epilogue (each CTA) ========
+    // Identical to the role-split softmax of the single-CTA dual pass, on this CTA's own query tile and
+    // tensor memory; only the arrivals the leader's MMA warp waits for go to the leader's barriers.
+    {
+      const bool p_role = warp < 6;
+      const int quarter = warp & 3;
+      const int row = quarter * 32 + lane;
+      const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+      const uint32_t t_s = tmem + lane_base + TR::kColS, t_ds = tmem + lane_base + TR::kColDS;
+      const uint32_t t_p = tmem + lane_base + TR::kColP, t_o = tmem + lane_base + TR::kColO;
+      const float sl2 = p.scale_log2e;
+      float* xalpha = xchg;        // [block parity][row]: factor the P warps applied to the accumulators
+      float* xsum = xchg + 256;    // [l | mu][row]
+      uint32_t gblk = 0, xuse = 0;
+      bool ok = true;
+      auto wait = [&](int b_, uint32_t parity) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleSoftmax + b_));
+      };
+      for (int pp = cluster_id; ok && pp < p.num_tiles; pp += num_clusters) {
+        const int bh = pp / pairs_per_bh;
+        const int q0 = (2 * (pp % pairs_per_bh) + static_cast<int>(rank)) * kBlockQ;
+        const int b = bh / p.heads, h = bh % p.heads;
+        float m_used = -CUDART_INF_F, l = 0.f, mu = 0.f;
+        for (int j = 0; j < num_kv_blocks; ++j, ++gblk) {
+          if (p_role) {
+            // ---- S -> P ------------------------------------------------------
+            ok = wait(TR::kBarSFull, gblk & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t r[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, r[c]);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive_warp_cluster(lbar(TR::kBarSEmpty));  // S is in registers (the leader waits for both CTAs)
+            float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                mx0 = max3(mx0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                mx1 = max3(mx1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+                mx2 = max3(mx2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+                mx3 = max3(mx3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
+              }
+            }
+            const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+            float alpha = 1.f;
+            if (j == 0) {
+              m_used = m_blk;
+            } else {
+              const bool need = m_blk > m_used + kRescaleThreshold;
+              if (__any_sync(0xffffffffu, need)) {
+                // every MMA that accumulated into O / T for the previous blocks must be done: the
+                // commit of block g-2 is complete (S of this block was issued after it), so the
+                // barrier is at most one phase ahead
+                ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (need) {
+                  alpha = fast_exp2(m_used - m_blk);
+                  m_used = m_blk;
+                }
+                l *= alpha;
+#pragma unroll 1
+                for (int c = 0; c < 2 * DPAD / 16; ++c) {
+                  uint32_t a[16];
+                  tmem_ld_x16(t_o + c * 16, a);
+                  tmem_wait_ld();
+#pragma unroll
+                  for (int i = 0; i < 16; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) * alpha);
+                  tmem_st_x16(t_o + c * 16, a);
+                }
+                tmem_wait_st();
+              }
+            }
+            xalpha[(gblk & 1u) * 128 + row] = alpha;  // the G warps scale mu by the same factor
+            const uint64_t sl2_2 = pack_f2(sl2, sl2), neg_m2 = pack_f2(-m_used, -m_used);
+            uint64_t la = pack_f2(0.f, 0.f), lb = la;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float x0, x1, p2, p3;
+                unpack_f2(fma2(pack_u2(r[c][i], r[c][i + 1]), sl2_2, neg_m2), x0, x1);
+                const uint64_t xb = fma2(pack_u2(r[c][i + 2], r[c][i + 3]), sl2_2, neg_m2);
+                if (kPolyEvery > 0 && ((i / 4) % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery - 1)) {
+                  poly_exp2_x2(xb, p2, p3);  // FMA-pipe cubic
+                } else {
+                  float x2, x3;
+                  unpack_f2(xb, x2, x3);
+                  p2 = fast_exp2(x2);
+                  p3 = fast_exp2(x3);
+                }
+                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                la = add2(la, pack_f2(p0, p1));
+                lb = add2(lb, pack_f2(p2, p3));
+                r[c][i / 2] = Pack2<T>::pack(p0, p1);       // packed in place: word k holds elements 2k, 2k+1
+                r[c][i / 2 + 1] = Pack2<T>::pack(p2, p3);
+              }
+            }
+            {
+              float s0, s1;
+              unpack_f2(add2(la, lb), s0, s1);
+              l += s0 + s1;
+            }
+            if (gblk > 0) {  // the P V products of the previous block and the G warps have read P
+              ok = wait(TR::kBarPEmpty, (gblk - 1u) & 1u);
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pk[i] = r[c][i];
+              tmem_st_x16(t_p + c * 16, pk);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive_warp_cluster(lbar(TR::kBarPFull));  // for the MMA warp of the leader
+            mbar_arrive_warp(bar(TR::kBarPG));                // for this CTA's G warps
+          } else {
+            // ---- G = P * dS * scale, mu += rowsum(G) ---------------------------
+            ok = wait(TR::kBarDSFull, gblk & 1u);
+            if (!ok) break;
+            ok = wait(TR::kBarPG, gblk & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            mu *= xalpha[(gblk & 1u) * 128 + row];
+            const uint64_t scale2 = pack_f2(p.scale, p.scale);
+            uint64_t mua = pack_f2(0.f, 0.f), mub = mua;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t d[32], pp[16];
+              tmem_ld_x32(t_ds + c * 32, d);
+              tmem_ld_x16(t_p + c * 16, pp);
+              tmem_wait_ld();
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; i += 2) {
+                const float2 pa = unpack2<T>(pp[i]), pb = unpack2<T>(pp[i + 1]);
+                const uint64_t ga = mul2(pack_f2(pa.x, pa.y), mul2(pack_u2(d[2 * i], d[2 * i + 1]), scale2));
+                const uint64_t gb = mul2(pack_f2(pb.x, pb.y), mul2(pack_u2(d[2 * i + 2], d[2 * i + 3]), scale2));
+                mua = add2(mua, ga);
+                mub = add2(mub, gb);
+                float g0, g1, g2, g3;
+                unpack_f2(ga, g0, g1);
+                unpack_f2(gb, g2, g3);
+                pk[i] = Pack2<T>::pack(g0, g1);
+                pk[i + 1] = Pack2<T>::pack(g2, g3);
+              }
+              tmem_st_x16(t_ds + c * 16, pk);  // over dS columns this thread has already read
+            }
+            {
+              float s0, s1;
+              unpack_f2(add2(mua, mub), s0, s1);
+              mu += s0 + s1;
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive_warp(bar(TR::kBarPEmpty));  // P has been read
+            mbar_arrive_warp_cluster(lbar(TR::kBarGFull));
+          }
+        }
+        if (!ok) break;
+        // ---- epilogue: combine l and mu, normalise, write o, to, lse --------------
+        // The meeting comes first: a G warp only gets here after it has seen dS of the last block,
+        // which was issued after the G V product of the block before, so once everybody has met the
+        // accumulator barrier is at most one phase ahead of any waiter.
+        xsum[(p_role ? 0 : 128) + row] = p_role ? l : mu;
+        mbar_arrive_warp(bar(TR::kBarXchg));
+        ok = wait(TR::kBarXchg, xuse & 1u);
+        ++xuse;
+        if (!ok) break;
+        ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const float l_tot = xsum[row], mu_tot = xsum[128 + row];
+        const float inv_l = 1.f / l_tot;
+        const float mu_n = mu_tot * inv_l;
+        const int64_t lq = q0 + row;
+        T* o_row = reinterpret_cast<T*>(p.o) + b * p.o_sb + lq * p.o_sl + h * p.o_sh;
+        T* to_row = reinterpret_cast<T*>(p.to) + b * p.to_sb + lq * p.to_sl + h * p.to_sh;
+#pragma unroll
+        for (int c = 0; c < DPAD / 16; ++c) {
+          if ((c & 1) != (p_role ? 0 : 1)) continue;  // the two groups alternate 16-column chunks
+          uint32_t a[16], t[16];
+          tmem_ld_x16(t_o + c * 16, a);
+          tmem_ld_x16(t_o + DPAD + c * 16, t);
+          tmem_wait_ld();
+          uint32_t po[8], pt[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float o0 = __uint_as_float(a[2 * i]) * inv_l;
+            const float o1 = __uint_as_float(a[2 * i + 1]) * inv_l;
+            po[i] = Pack2<T>::pack(o0, o1);
+            const float t0 = fmaf(__uint_as_float(t[2 * i]), inv_l, -mu_n * o0);
+            const float t1 = fmaf(__uint_as_float(t[2 * i + 1]), inv_l, -mu_n * o1);
+            pt[i] = Pack2<T>::pack(t0, t1);
+          }
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int cc = pair_head_col<TR>(c * 16 + hh * 8);  // accumulator column -> head-dim column
+            if (cc < p.head_dim) {
+              *reinterpret_cast<uint4*>(o_row + cc) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
+              *reinterpret_cast<uint4*>(to_row + cc) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
+            }
+          }
+        }
+        if (p_role)
+          p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seqlen_q + lq] =
+              (m_used + __log2f(l_tot)) * 0.6931471805599453f;
+        tc_fence_before_sync();
+      }
+
+    }
+  }
+
+  // ============================== teardown ==================================
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves (or frees tensor memory) while the other CTA may still touch this one
+  tc_fence_after_sync();
+  if (warp == 0) tmem_dealloc_pair(tmem, TR::kTmemCols);
+}
+
+}  // namespace dmf

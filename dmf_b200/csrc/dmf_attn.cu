@@ -8,10 +8,13 @@
 
 #include <atomic>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "attn_bwd.cuh"
 #include "attn_fwd.cuh"
+#include "attn_fwd_pair.cuh"
 
 namespace {
 
@@ -186,6 +189,61 @@ int launch_fwd_tail(const FwdParams& p, int tail, int grid, cudaStream_t stream)
   }
 }
 
+// ---- forward launch, CTA-pair variant (dual pass, head_dim <= 96, even number of query tiles) ----
+
+template <typename T, int TAIL>
+int launch_pair_inst(const FwdParams& p, int clusters, cudaStream_t stream) {
+  using TR = PairTraits<TAIL>;
+  auto kernel = attn_fwd_pair_kernel<T, TAIL>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::kSmemBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_LAUNCH;
+  }
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(kPairThreads, 1, 1);
+  cfg.dynamicSmemBytes = TR::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (std::getenv("DMF_ATTN_DEBUG") != nullptr) {
+    int n = -1;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+    std::fprintf(stderr, "[dmf_attn] pair kernel: %d clusters requested, max active clusters %d (%s)\n", clusters, n,
+                 cudaGetErrorString(e));
+  }
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_LAUNCH;
+  }
+  return DMF_ATTN_OK;
+}
+
+template <typename T>
+int launch_pair_tail(const FwdParams& p, int tail, int clusters, cudaStream_t stream) {
+  switch (tail) {
+    case 0: return launch_pair_inst<T, 0>(p, clusters, stream);
+    case 16: return launch_pair_inst<T, 16>(p, clusters, stream);
+    case 32: return launch_pair_inst<T, 32>(p, clusters, stream);
+    default: return DMF_ATTN_ERR_HEAD_DIM;
+  }
+}
+
+// DMF_ATTN_PAIR=0 in the environment keeps the single-CTA kernel (for comparisons).
+bool pair_kernel_enabled() {
+  static const bool enabled = [] {
+    const char* e = std::getenv("DMF_ATTN_PAIR");
+    return e == nullptr || e[0] != '0';
+  }();
+  return enabled;
+}
+
 int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
   int st = validate_fwd(a, dual);
   if (st != DMF_ATTN_OK) return st;
@@ -197,11 +255,14 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
   std::memset(&p, 0, sizeof(p));
   const int B = a->batch, H = a->heads, D = a->head_dim, Lq = a->seqlen_q, Lk = a->seqlen_kv, dt = a->dtype;
   if ((st = make_map_pair(&p.q_main, &p.q_tail, a->q, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
-  if ((st = make_map_pair(&p.k_main, &p.k_tail, a->k, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
+  // CTA-pair kernel: dual pass, P in its own tensor-memory columns (head_dim <= 96), tiles pair up
+  const bool pair = dual && tail <= 32 && ((Lq / kBlockQ) % 2 == 0) && pair_kernel_enabled();
+  const int k_box_rows = pair ? kBlockKV / 2 : kBlockKV;  // a CTA of a pair loads half of the key rows
+  if ((st = make_map_pair(&p.k_main, &p.k_tail, a->k, dt, B, Lk, H, D, tail, k_box_rows)) != DMF_ATTN_OK) return st;
   if ((st = make_map(&p.v_map, a->v, dt, B, Lk, H, D, 32, kBlockKV, CU_TENSOR_MAP_SWIZZLE_64B)) != DMF_ATTN_OK) return st;
   if (dual) {
     if ((st = make_map_pair(&p.tq_main, &p.tq_tail, a->tq, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
-    if ((st = make_map_pair(&p.tk_main, &p.tk_tail, a->tk, dt, B, Lk, H, D, tail, kBlockKV)) != DMF_ATTN_OK) return st;
+    if ((st = make_map_pair(&p.tk_main, &p.tk_tail, a->tk, dt, B, Lk, H, D, tail, k_box_rows)) != DMF_ATTN_OK) return st;
     if ((st = make_map(&p.tv_map, a->tv, dt, B, Lk, H, D, 32, kBlockKV, CU_TENSOR_MAP_SWIZZLE_64B)) != DMF_ATTN_OK) return st;
   }
   p.o = a->o.ptr;
@@ -242,8 +303,16 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
       p.align0[g] = ref[0]; p.align_b[g] = ref[1]; p.align_h[g] = ref[2];
     }
   }
-  const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (pair) {
+    p.align_enable[1] = 0;  // the pair kernel's V column order has no room for the 8-column shift
+    p.num_tiles /= 2;       // tile pairs
+    const int max_clusters = sm_count / 2;
+    const int clusters = p.num_tiles < max_clusters ? p.num_tiles : max_clusters;
+    return dt == DMF_ATTN_BF16 ? launch_pair_tail<__nv_bfloat16>(p, tail, clusters, stream)
+                               : launch_pair_tail<__half>(p, tail, clusters, stream);
+  }
+  const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
   if (dt == DMF_ATTN_BF16)
     return dual ? launch_fwd_tail<__nv_bfloat16, true>(p, tail, grid, stream)
                 : launch_fwd_tail<__nv_bfloat16, false>(p, tail, grid, stream);
