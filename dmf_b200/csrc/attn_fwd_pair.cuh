@@ -260,27 +260,32 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           issue_qk_pair<TAIL, TR>(leader, t_s, s_q, kt, idesc_qk, false);
           commit(TR::kBarSFull);
           ++scnt;
+          ++kcnt;
           return true;
         };
-        auto issue_ds = [&](bool last_of_tile) {
-          issue_qk_pair<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, kt, idesc_qk, false);
-          issue_qk_pair<TAIL, TR>(leader, t_ds, s_q, kt + TR::kKTileBytes, idesc_qk, true);
-          commit(TR::kBarDSFull);
-          commit(TR::kBarKEmpty + sk);
-          ++kcnt;
-          if (last_of_tile) commit(TR::kBarQEmpty);
-        };
-        ok = issue_s();
+        // Issue order per tile (S runs two blocks ahead of the P V products, which the three-stage K ring
+        // allows):  S_0 dS_0 S_1 | P V_0, P dV_0, S_2, G V_0, dS_1 | P V_1, P dV_1, S_3, G V_1, dS_2 | ...
+        // dS_j uses the K block that S_j used; S_{j+2} may only overwrite S_{j+1} once the softmax of both
+        // CTAs has it in registers.
+        uint32_t ds_sk = 0, ds_kt = 0;       // ring slot / address of the K block the next dS will use
+        ok = issue_s();                      // S_0
         if (!ok) break;
-        issue_ds(num_kv_blocks == 1);
+        ds_sk = sk; ds_kt = kt;
+        {
+          issue_qk_pair<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, ds_kt, idesc_qk, false);   // dS_0
+          issue_qk_pair<TAIL, TR>(leader, t_ds, s_q, ds_kt + TR::kKTileBytes, idesc_qk, true);
+          commit(TR::kBarDSFull);
+          commit(TR::kBarKEmpty + ds_sk);
+          if (num_kv_blocks == 1) commit(TR::kBarQEmpty);
+        }
+        if (num_kv_blocks > 1) {
+          ok = issue_s();                    // S_1
+          if (!ok) break;
+          ds_sk = sk; ds_kt = kt;            // dS_1 will use this K block
+        }
         for (int j = 0; j < num_kv_blocks; ++j) {
           const uint32_t sv = vcnt % TR::kStagesV;
           const uint32_t vt = s_v + sv * TR::kVGroupBytes;
-          const bool more = (j + 1 < num_kv_blocks);
-          if (more) {
-            ok = issue_s();
-            if (!ok) break;
-          }
           ok = wait(TR::kBarVFull + sv, (vcnt / TR::kStagesV) & 1u);
           if (!ok) break;
           ok = wait(TR::kBarPFull, pcnt & 1u);
@@ -290,6 +295,13 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           issue_pv_pair<TR>(leader, t_o, t_p, vt, idesc_pv, j > 0);                    // O += P V
           issue_pv_pair<TR>(leader, t_t, t_p, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
           commit(TR::kBarPEmpty);
+          uint32_t nx_sk = 0, nx_kt = 0;
+          const bool s_ahead = (j + 2 < num_kv_blocks);
+          if (s_ahead) {
+            ok = issue_s();                  // S_{j+2}
+            if (!ok) break;
+            nx_sk = sk; nx_kt = kt;
+          }
           ok = wait(TR::kBarGFull, gcnt & 1u);
           if (!ok) break;
           ++gcnt;
@@ -298,7 +310,14 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           commit(TR::kBarAccFull);
           commit(TR::kBarVEmpty + sv);
           ++vcnt;
-          if (more) issue_ds(j + 2 == num_kv_blocks);
+          if (j + 1 < num_kv_blocks) {       // dS_{j+1}, on the K block S_{j+1} used
+            issue_qk_pair<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, ds_kt, idesc_qk, false);
+            issue_qk_pair<TAIL, TR>(leader, t_ds, s_q, ds_kt + TR::kKTileBytes, idesc_qk, true);
+            commit(TR::kBarDSFull);
+            commit(TR::kBarKEmpty + ds_sk);
+            if (j + 2 == num_kv_blocks) commit(TR::kBarQEmpty);
+          }
+          ds_sk = nx_sk; ds_kt = nx_kt;
         }
       }
     }
