@@ -567,24 +567,32 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             mbar_arrive_warp(bar(TR::kBarPFull));
           } else {
             // ---- G = P * dS * scale, mu += rowsum(G) ---------------------------
-            ok = wait(TR::kBarDSFull, gblk & 1u);
-            if (!ok) break;
+            // P first: it is ready long before dS, and once it sits in registers its columns can be
+            // handed back to the P warps (they would otherwise wait for this whole block of G work).
             ok = wait(TR::kBarPFull, gblk & 1u);
             if (!ok) break;
             tc_fence_after_sync();
+            uint32_t pp[4][16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_x16(t_p + c * 16, pp[c]);
+            tmem_wait_ld();
+            tc_fence_before_sync();
             mu *= xalpha[(gblk & 1u) * 128 + row];
+            mbar_arrive_warp(bar(TR::kBarPEmpty));  // P has been read
+            ok = wait(TR::kBarDSFull, gblk & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
             const uint64_t scale2 = pack_f2(p.scale, p.scale);
             uint64_t mua = pack_f2(0.f, 0.f), mub = mua;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-              uint32_t d[32], pp[16];
+              uint32_t d[32];
               tmem_ld_x32(t_ds + c * 32, d);
-              tmem_ld_x16(t_p + c * 16, pp);
               tmem_wait_ld();
               uint32_t pk[16];
 #pragma unroll
               for (int i = 0; i < 16; i += 2) {
-                const float2 pa = unpack2<T>(pp[i]), pb = unpack2<T>(pp[i + 1]);
+                const float2 pa = unpack2<T>(pp[c][i]), pb = unpack2<T>(pp[c][i + 1]);
                 const uint64_t ga = mul2(pack_f2(pa.x, pa.y), mul2(pack_u2(d[2 * i], d[2 * i + 1]), scale2));
                 const uint64_t gb = mul2(pack_f2(pb.x, pb.y), mul2(pack_u2(d[2 * i + 2], d[2 * i + 3]), scale2));
                 mua = add2(mua, ga);
@@ -604,7 +612,6 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             }
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive_warp(bar(TR::kBarPEmpty));  // P has been read
             mbar_arrive_warp(bar(TR::kBarGFull));
           }
         }
