@@ -44,6 +44,7 @@ WORKLOADS = {
     "C2": (256, 256, 16, 72, 0.1, False, "attention JVP fwd+tangent, SiT-XL/2 256px: B=256 H=16 N=256 D=72"),
 }
 CPU_SAMPLE_BATCH = 2  # batch slice of the workload one CPU step computes
+CPU_SAMPLE_SECONDS = 12.0  # CPU work the cpu_baseline leg aims for
 
 
 def _flops(B, L, H, D):
@@ -63,6 +64,18 @@ def _peaks():
     return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
+def _kernel_name(op, D, L):
+    """Name of the kernel instance the library picks for this shape (same rule as the launcher)."""
+    tail = ((D + 15) // 16) * 16 - 64
+    if op == "dual":
+        pair = tail <= 32 and (L // 128) % 2 == 0 and os.environ.get("DMF_ATTN_PAIR", "1") != "0"
+        return (f"attn_fwd_pair_kernel<bf16, TAIL={tail}> (cta_group::2 cluster pair)" if pair
+                else f"attn_fwd_kernel<bf16, TAIL={tail}, dual>")
+    if op == "fwd":
+        return f"attn_fwd_kernel<bf16, TAIL={tail}, plain>"
+    return f"attn_bwd_kernel<bf16, TAIL={tail}, dQ> + attn_bwd_kernel<bf16, TAIL={tail}, dK/dV>"
+
+
 def _traffic(workload):
     """DRAM bytes per launch from the committed ncu capture of this kernel, or None."""
     p = ROOT / "profiles" / "dram_traffic.json"
@@ -74,7 +87,7 @@ def _traffic(workload):
 class ClockSampler(threading.Thread):
     """Reads (never sets) SM clock and throttle reasons through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.005):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
@@ -308,8 +321,7 @@ def run_ours(args):
         "frac_of_nominal_2250": achieved / 2250.0,
         "algorithmic_flops_per_launch": fl, "algorithmic_bytes_per_launch": algo_bytes,
         "hbm_gbs_achieved": algo_bytes / (ms_step * 1e-3) / 1e9,
-        "kernel": {"dual": "attn_fwd_kernel<bf16, TAIL=16, dual>", "fwd": "attn_fwd_kernel<bf16, TAIL=16, plain>",
-                   "bwd": "attn_bwd_kernel<bf16, TAIL=16, dQ> + attn_bwd_kernel<bf16, TAIL=16, dK/dV>"}[op],
+        "kernel": _kernel_name(op, D, L),
     }
 
     cpu_base = None
@@ -318,11 +330,13 @@ def run_ours(args):
         torch.set_num_threads(cores)
         cstep, cfl = _cpu_step_fn(args.workload, CPU_SAMPLE_BATCH)
         t0 = time.perf_counter()
-        times = _time_cpu(cstep, 5, 1)
+        first = _time_cpu(cstep, 1, 1)[0]
+        n_cpu = int(min(200, max(5, round(CPU_SAMPLE_SECONDS / max(first, 1e-3)))))
+        times = _time_cpu(cstep, n_cpu, 0)
         cpu_base = {
             "value": cfl * len(times) / sum(times) / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),
             "kind": "port",
-            "sample": f"5 runs of a B={CPU_SAMPLE_BATCH} batch slice of {args.workload} ({cfl / 1e9:.1f} GFLOP each), "
+            "sample": f"{n_cpu} runs of a B={CPU_SAMPLE_BATCH} batch slice of {args.workload} ({cfl / 1e9:.1f} GFLOP each), "
                       f"fp32 'base' attention under torch.func.jvp, {time.perf_counter() - t0:.1f} s of CPU work",
         }
 
@@ -380,7 +394,7 @@ def run_model(args):
     sampler = ClockSampler(local_rank)
     sampler.start()
     warm = max(args.warmup, 3) if args.warmup != 10 else 3
-    steps = args.steps if args.steps != 200 else (5 if args.workload == "C4" else 10)
+    steps = args.steps if args.steps != 50 else (5 if args.workload == "C4" else 10)
 
     if args.workload == "C4":
         global_batch, mb = 256, args.micro_batch
@@ -470,7 +484,7 @@ def run_model(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=list(WORKLOADS) + ["C4", "C5"], default="C3",
