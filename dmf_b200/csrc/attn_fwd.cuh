@@ -62,6 +62,8 @@ struct FwdParams {
   CUtensorMap tq_main, tq_tail, tk_main, tk_tail;
   // V and dV: boxes of 32 columns x 128 rows with 64-byte swizzle ("atoms"), see FwdTraits
   CUtensorMap v_map, tv_map;
+  // outputs as TMA store maps (boxes of 128 rows; only the CTA-pair kernel stores through them)
+  CUtensorMap o_main, o_tail, to_main, to_tail;
   void* o;
   void* to;
   float* lse;

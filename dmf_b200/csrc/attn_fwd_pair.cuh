@@ -32,6 +32,13 @@
 
 namespace dmf {
 
+#ifndef DMF_PAIR_VSTAGES16
+#define DMF_PAIR_VSTAGES16 3
+#endif
+#ifndef DMF_PAIR_OUTBUFS16
+#define DMF_PAIR_OUTBUFS16 1
+#endif
+
 template <int TAIL>
 struct PairTraits {
   static_assert(TAIL == 0 || TAIL == 16 || TAIL == 32, "the pair kernel needs P in its own tensor-memory columns");
@@ -53,15 +60,22 @@ struct PairTraits {
   static constexpr int kVAtomBytes = 128 * 64;
   static constexpr int kVTileBytes = kVAtoms * kVAtomBytes;
   static constexpr int kVGroupBytes = 2 * kVTileBytes;
-  static constexpr int kStagesK = 3, kStagesV = 3;
-  static constexpr int kTileSmem = kQGroupBytes + kStagesK * kKGroupBytes + kStagesV * kVGroupBytes;
-  static constexpr int kXchgBytes = 2048;
+  // Ring depths and output staging (one tile-shaped buffer each for o and to, or one shared by both)
+  // are what fits in 227 KB: head_dim 96 has room for two V stages and one staging buffer only.
+  static constexpr int kStagesK = 3;
+  static constexpr int kStagesV = TAIL == 32 ? 2 : (TAIL == 16 ? DMF_PAIR_VSTAGES16 : 3);
+  static constexpr int kOutBufs = TAIL == 32 ? 1 : (TAIL == 16 ? DMF_PAIR_OUTBUFS16 : 2);
+  static constexpr int kRingBytes = kQGroupBytes + kStagesK * kKGroupBytes + kStagesV * kVGroupBytes;
+  static constexpr int kTileSmem = kRingBytes + kOutBufs * kTileBytes;
+  static constexpr int kXchgBytes = 4096;
   // barriers
   static constexpr int kBarQFull = 0, kBarQEmpty = 1, kBarSFull = 2, kBarDSFull = 3, kBarPFull = 4, kBarGFull = 5,
-                       kBarAccFull = 6, kBarXchg = 7, kBarSEmpty = 8, kBarPEmpty = 9, kBarPG = 10, kBarKFull = 11,
+                       kBarAccFull = 6, kBarXchg = 7, kBarSEmpty = 8, kBarPEmpty = 9, kBarPG = 10, kBarAccEmpty = 11,
+                       kBarKFull = 12,
                        kBarKEmpty = kBarKFull + kStagesK, kBarVFull = kBarKEmpty + kStagesK,
                        kBarVEmpty = kBarVFull + kStagesV, kNumBars = kBarVEmpty + kStagesV;
   static constexpr int kSmemBytes = 1024 + kTileSmem + kXchgBytes + kNumBars * 8 + 16;
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
   // tensor memory columns (per CTA)
   static constexpr uint32_t kColS = 0, kColDS = 128, kColP = 256, kColO = 320, kColT = 320 + kDPad;
   static constexpr uint32_t kTmemCols = 512;
@@ -127,6 +141,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
   const uint32_t s_q = smem_u32(smem);
   const uint32_t s_k = s_q + TR::kQGroupBytes;
   const uint32_t s_v = s_k + TR::kStagesK * TR::kKGroupBytes;
+  uint8_t* out_stage = smem + TR::kRingBytes;  // tile-shaped staging for the TMA stores of o and to
   float* xchg = reinterpret_cast<float*>(smem + TR::kTileSmem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TR::kTileSmem + TR::kXchgBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + TR::kNumBars);
@@ -148,8 +163,9 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
       uint32_t count = 1;  // tcgen05.commit (multicast from the leader)
       if (i == TR::kBarQFull || (i >= TR::kBarKFull && i < TR::kBarKEmpty) || (i >= TR::kBarVFull && i < TR::kBarVEmpty))
         count = 2;  // one producer arrival (+ its transaction bytes) per CTA
-      if (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarSEmpty) count = 8;  // 4 warps of each CTA
-      if (i == TR::kBarXchg) count = 8;    // the 8 local softmax warps
+      if (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarSEmpty || i == TR::kBarAccEmpty)
+        count = 8;                         // 4 warps of each CTA
+      if (i == TR::kBarXchg) count = 4;    // the 4 local P warps
       if (i == TR::kBarPG) count = 4;      // the 4 local P warps
       if (i == TR::kBarPEmpty) count = 5;  // commit + the 4 local G warps
       mbar_init(bar(i), count);
@@ -291,6 +307,10 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           ok = wait(TR::kBarPFull, pcnt & 1u);
           if (!ok) break;
           ++pcnt;
+          if (j == 0 && tcnt > 0) {  // the epilogue of the previous tile pair has read O and T (both CTAs)
+            ok = wait(TR::kBarAccEmpty, (tcnt - 1u) & 1u);
+            if (!ok) break;
+          }
           tc_fence_after_sync();
           issue_pv_pair<TR>(leader, t_o, t_p, vt, idesc_pv, j > 0);                    // O += P V
           issue_pv_pair<TR>(leader, t_t, t_p, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
@@ -334,13 +354,14 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
       const uint32_t t_p = tmem + lane_base + TR::kColP, t_o = tmem + lane_base + TR::kColO;
       const float sl2 = p.scale_log2e;
       float* xalpha = xchg;        // [block parity][row]: factor the P warps applied to the accumulators
-      float* xsum = xchg + 256;    // [l | mu][row]
-      uint32_t gblk = 0, xuse = 0;
+      float* xl = xchg + 256;      // [tile parity][row]: row sum l of the finished tile, for the G warps
+      float* xm = xchg + 512;      // [tile parity][row]: running maximum of the finished tile
+      uint32_t gblk = 0, tcnt = 0;
       bool ok = true;
       auto wait = [&](int b_, uint32_t parity) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleSoftmax + b_));
       };
-      for (int pp = cluster_id; ok && pp < p.num_tiles; pp += num_clusters) {
+      for (int pp = cluster_id; ok && pp < p.num_tiles; pp += num_clusters, ++tcnt) {
         const int bh = pp / pairs_per_bh;
         const int q0 = (2 * (pp % pairs_per_bh) + static_cast<int>(rank)) * kBlockQ;
         const int b = bh / p.heads, h = bh % p.heads;
@@ -494,57 +515,97 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
             mbar_arrive_warp_cluster(lbar(TR::kBarGFull));
           }
         }
-        if (!ok) break;
-        // ---- epilogue: combine l and mu, normalise, write o, to, lse --------------
-        // The meeting comes first: a G warp only gets here after it has seen dS of the last block,
-        // which was issued after the G V product of the block before, so once everybody has met the
-        // accumulator barrier is at most one phase ahead of any waiter.
-        xsum[(p_role ? 0 : 128) + row] = p_role ? l : mu;
-        mbar_arrive_warp(bar(TR::kBarXchg));
-        ok = wait(TR::kBarXchg, xuse & 1u);
-        ++xuse;
-        if (!ok) break;
-        ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+        // ---- end of the tile ------------------------------------------------------
+        // The P warps hand l and the running maximum to the G warps and go straight on to the next
+        // tile; the G warps alone normalise and store (they would otherwise idle until the first
+        // P and dS of the next tile exist).
+        if (p_role) {
+          if (!ok) break;
+          xl[(tcnt & 1u) * 128 + row] = l;
+          xm[(tcnt & 1u) * 128 + row] = m_used;
+          mbar_arrive_warp(bar(TR::kBarXchg));
+          continue;
+        }
+        // A G warp only gets here after it has seen dS of the last block, which was issued after the
+        // G V product of the block before, so the accumulator barrier is at most one phase ahead.
+        if (ok) ok = wait(TR::kBarXchg, tcnt & 1u);
+        if (ok) ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+        // the staging tile of the previous pair must have been read by its store
+        if (warp == 6 && lane == 0) tma_store_wait_read();
+        ok = named_bar_and(1, 128, ok);  // every G warp arrives here, whatever happened to its waits
         if (!ok) break;
         tc_fence_after_sync();
-        const float l_tot = xsum[row], mu_tot = xsum[128 + row];
+        const float l_tot = xl[(tcnt & 1u) * 128 + row], mu_tot = mu;
         const float inv_l = 1.f / l_tot;
         const float mu_n = mu_tot * inv_l;
         const int64_t lq = q0 + row;
-        T* o_row = reinterpret_cast<T*>(p.o) + b * p.o_sb + lq * p.o_sl + h * p.o_sh;
-        T* to_row = reinterpret_cast<T*>(p.to) + b * p.to_sb + lq * p.to_sl + h * p.to_sh;
+        p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seqlen_q + lq] =
+            (xm[(tcnt & 1u) * 128 + row] + __log2f(l_tot)) * 0.6931471805599453f;
+        // Staging tiles have the layout of a TMA box pair: 64 columns with the 128-byte swizzle, then
+        // TAIL columns with the tail's swizzle; 16-byte chunk c of row r sits at chunk c ^ f(r).
+        uint8_t* st_o = out_stage;
+        uint8_t* st_t = out_stage + (TR::kOutBufs - 1) * TR::kTileBytes;
+        auto chunk_off = [&](int cc) -> uint32_t {  // cc: head-dim column, a multiple of 8
+          if (cc < 64) return static_cast<uint32_t>(row * 128 + (((cc >> 3) ^ (row & 7)) << 4));
+          const int ct = (cc - 64) >> 3;
+          if constexpr (TAIL == 32)
+            return static_cast<uint32_t>(TR::kMainBytes + row * 64 + ((ct ^ ((row >> 1) & 3)) << 4));
+          else
+            return static_cast<uint32_t>(TR::kMainBytes + row * 32 + ((ct ^ ((row >> 2) & 1)) << 4));
+        };
 #pragma unroll
-        for (int c = 0; c < DPAD / 16; ++c) {
-          if ((c & 1) != (p_role ? 0 : 1)) continue;  // the two groups alternate 16-column chunks
-          uint32_t a[16], t[16];
-          tmem_ld_x16(t_o + c * 16, a);
-          tmem_ld_x16(t_o + DPAD + c * 16, t);
-          tmem_wait_ld();
-          uint32_t po[8], pt[8];
+        for (int pass = 0; pass < (TR::kOutBufs == 1 ? 2 : 1); ++pass) {
+          const bool do_o = TR::kOutBufs == 2 || pass == 0;
+          const bool do_t = TR::kOutBufs == 2 || pass == 1;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float o0 = __uint_as_float(a[2 * i]) * inv_l;
-            const float o1 = __uint_as_float(a[2 * i + 1]) * inv_l;
-            po[i] = Pack2<T>::pack(o0, o1);
-            const float t0 = fmaf(__uint_as_float(t[2 * i]), inv_l, -mu_n * o0);
-            const float t1 = fmaf(__uint_as_float(t[2 * i + 1]), inv_l, -mu_n * o1);
-            pt[i] = Pack2<T>::pack(t0, t1);
-          }
+          for (int c = 0; c < DPAD / 16; ++c) {
+            uint32_t a[16], t[16];
+            tmem_ld_x16(t_o + c * 16, a);
+            if (do_t) tmem_ld_x16(t_o + DPAD + c * 16, t);
+            tmem_wait_ld();
+            uint32_t po[8], pt[8];
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            const int cc = pair_head_col<TR>(c * 16 + hh * 8);  // accumulator column -> head-dim column
-            if (cc < p.head_dim) {
-              *reinterpret_cast<uint4*>(o_row + cc) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
-              *reinterpret_cast<uint4*>(to_row + cc) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
+            for (int i = 0; i < 8; ++i) {
+              const float o0 = __uint_as_float(a[2 * i]) * inv_l;
+              const float o1 = __uint_as_float(a[2 * i + 1]) * inv_l;
+              po[i] = Pack2<T>::pack(o0, o1);
+              if (do_t) {
+                const float t0 = fmaf(__uint_as_float(t[2 * i]), inv_l, -mu_n * o0);
+                const float t1 = fmaf(__uint_as_float(t[2 * i + 1]), inv_l, -mu_n * o1);
+                pt[i] = Pack2<T>::pack(t0, t1);
+              }
+            }
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              const uint32_t off = chunk_off(pair_head_col<TR>(c * 16 + hh * 8));  // accumulator -> head-dim column
+              if (do_o)
+                *reinterpret_cast<uint4*>(st_o + off) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
+              if (do_t)
+                *reinterpret_cast<uint4*>(st_t + off) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
             }
           }
+          if (do_t) {  // O and T are in registers / shared memory: the next tile may overwrite them
+            tc_fence_before_sync();
+            mbar_arrive_warp_cluster(lbar(TR::kBarAccEmpty));
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (warp == 6 && lane == 0) {
+            if (do_o) {
+              tma_store_4d(&p.o_main, smem_u32(st_o), 0, q0, h, b);
+              if constexpr (TAIL > 0) tma_store_4d(&p.o_tail, smem_u32(st_o) + TR::kMainBytes, 64, q0, h, b);
+            }
+            if (do_t) {
+              tma_store_4d(&p.to_main, smem_u32(st_t), 0, q0, h, b);
+              if constexpr (TAIL > 0) tma_store_4d(&p.to_tail, smem_u32(st_t) + TR::kMainBytes, 64, q0, h, b);
+            }
+            tma_store_commit();
+            if (TR::kOutBufs == 1 && pass == 0) tma_store_wait_read();
+          }
+          if (TR::kOutBufs == 1 && pass == 0) named_bar_sync(1, 128);  // the shared tile is free for T
         }
-        if (p_role)
-          p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seqlen_q + lq] =
-              (m_used + __log2f(l_tot)) * 0.6931471805599453f;
-        tc_fence_before_sync();
       }
-
+      if (!p_role && warp == 6 && lane == 0) tma_store_wait_all();
     }
   }
 
