@@ -290,8 +290,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
         {
           issue_qk_pair<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, ds_kt, idesc_qk, false);   // dS_0
           issue_qk_pair<TAIL, TR>(leader, t_ds, s_q, ds_kt + TR::kKTileBytes, idesc_qk, true);
-          commit(TR::kBarDSFull);
-          commit(TR::kBarKEmpty + ds_sk);
+          commit(TR::kBarKEmpty + ds_sk);  // "dS ready" for the G warps and "K slot free" in one
           if (num_kv_blocks == 1) commit(TR::kBarQEmpty);
         }
         if (num_kv_blocks > 1) {
@@ -327,13 +326,11 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           ++gcnt;
           tc_fence_after_sync();
           issue_pv_pair<TR>(leader, t_t, t_ds, vt, idesc_pv, true);                    // T += G V
-          commit(TR::kBarAccFull);
-          commit(TR::kBarVEmpty + sv);
+          commit(TR::kBarVEmpty + sv);  // "accumulators up to date" for the softmax warps and "V slot free" in one
           ++vcnt;
           if (j + 1 < num_kv_blocks) {       // dS_{j+1}, on the K block S_{j+1} used
             issue_qk_pair<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, ds_kt, idesc_qk, false);
             issue_qk_pair<TAIL, TR>(leader, t_ds, s_q, ds_kt + TR::kKTileBytes, idesc_qk, true);
-            commit(TR::kBarDSFull);
             commit(TR::kBarKEmpty + ds_sk);
             if (j + 2 == num_kv_blocks) commit(TR::kBarQEmpty);
           }
@@ -360,6 +357,13 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
       bool ok = true;
       auto wait = [&](int b_, uint32_t parity) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleSoftmax + b_));
+      };
+      // Each tcgen05.commit costs the issuing thread about 120 cycles, so one commit serves two purposes:
+      // the barrier that frees V ring slot g % kStagesV also says that O and T hold everything up to
+      // block g, and the barrier that frees K ring slot g % kStagesK that dS of block g is ready
+      // (blocks are counted through all tile pairs of this cluster, like the ring slots).
+      auto wait_acc = [&](uint32_t g) -> bool {
+        return wait(TR::kBarVEmpty + g % TR::kStagesV, (g / TR::kStagesV) & 1u);
       };
       for (int pp = cluster_id; ok && pp < p.num_tiles; pp += num_clusters, ++tcnt) {
         const int bh = pp / pairs_per_bh;
@@ -399,7 +403,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
                 // every MMA that accumulated into O / T for the previous blocks must be done: the
                 // commit of block g-2 is complete (S of this block was issued after it), so the
                 // barrier is at most one phase ahead
-                ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+                ok = wait_acc(gblk - 1u);
                 if (!ok) break;
                 tc_fence_after_sync();
                 if (need) {
@@ -479,7 +483,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
             tc_fence_before_sync();
             mu *= xalpha[(gblk & 1u) * 128 + row];
             mbar_arrive_warp(bar(TR::kBarPEmpty));  // P has been read
-            ok = wait(TR::kBarDSFull, gblk & 1u);
+            ok = wait(TR::kBarKEmpty + gblk % TR::kStagesK, (gblk / TR::kStagesK) & 1u);  // dS of this block
             if (!ok) break;
             tc_fence_after_sync();
             const uint64_t scale2 = pack_f2(p.scale, p.scale);
@@ -529,7 +533,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
         // A G warp only gets here after it has seen dS of the last block, which was issued after the
         // G V product of the block before, so the accumulator barrier is at most one phase ahead.
         if (ok) ok = wait(TR::kBarXchg, tcnt & 1u);
-        if (ok) ok = wait(TR::kBarAccFull, (gblk - 1u) & 1u);
+        if (ok) ok = wait_acc(gblk - 1u);
         // the staging tile of the previous pair must have been read by its store
         if (warp == 6 && lane == 0) tma_store_wait_read();
         ok = named_bar_and(1, 128, ok);  // every G warp arrives here, whatever happened to its waits
