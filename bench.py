@@ -331,7 +331,7 @@ def run_ours(args):
         cstep, cfl = _cpu_step_fn(args.workload, CPU_SAMPLE_BATCH)
         t0 = time.perf_counter()
         first = _time_cpu(cstep, 1, 1)[0]
-        n_cpu = int(min(200, max(5, round(CPU_SAMPLE_SECONDS / max(first, 1e-3)))))
+        n_cpu = int(min(5000, max(5, round(CPU_SAMPLE_SECONDS / max(first, 1e-3)))))
         times = _time_cpu(cstep, n_cpu, 0)
         cpu_base = {
             "value": cfl * len(times) / sum(times) / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),

@@ -87,7 +87,8 @@ typedef struct dmf_attn_fwd_args {
  * Arguments of the primal backward.  grads of lse and of the tangent output are
  * not inputs: the reference drops them (stop-gradient on the tangent).
  * workspace: device memory of at least dmf_attn_bwd_workspace_bytes(); its
- * contents on entry do not matter (the call clears what it accumulates into).
+ * contents on entry do not matter (the first pass writes every word the second
+ * pass reads; nothing is accumulated in it).
  */
 typedef struct dmf_attn_bwd_args {
   int32_t batch;
