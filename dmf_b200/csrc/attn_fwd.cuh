@@ -107,7 +107,12 @@ struct FwdTraits {
   static constexpr int kVAtomBytes = 128 * 64;
   static constexpr int kVTileBytes = kVAtoms * kVAtomBytes;
   static constexpr int kVGroupBytes = kGroup * kVTileBytes;
-  static constexpr int kTileSmem = kGroupBytes * (1 + kStagesK_) + kVGroupBytes * kStagesV_;
+  // The plain forward stages its output tile in shared memory and writes it with TMA stores
+  // (thread-per-row 16-byte global stores touch 32 lines per instruction and stall the LSU for
+  // thousands of cycles per tile); the dual pass of this kernel has no room for that at head_dim 128.
+  static constexpr bool kStageOut = !kDual;
+  static constexpr int kRingBytes = kGroupBytes * (1 + kStagesK_) + kVGroupBytes * kStagesV_;
+  static constexpr int kTileSmem = kRingBytes + (kStageOut ? kTileBytes : 0);
   // barriers
   static constexpr int kBarQFull = 0, kBarQEmpty = 1, kBarSFull = 2, kBarDSFull = 3, kBarPFull = 4,
                        kBarGFull = 5, kBarAccFull = 6 /* and 7 */, kBarXchg = 8, kBarSEmpty = 9, kBarPEmpty = 10,
@@ -865,6 +870,8 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       tc_fence_after_sync();
       xsum[grp * 128 + row] = l;
       xsum[256 + grp * 128 + row] = mu;
+      // the staging tile of the previous tile must have been read by its store before anybody meets
+      if (TR::kStageOut && warp == 2 && lane == 0) tma_store_wait_read();
       ok = exchange();
       if (!ok) break;
       const float l_tot = l + xsum[(1 - grp) * 128 + row];
@@ -898,18 +905,45 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         for (int hh = 0; hh < 2; ++hh) {
           const int cc = c * 16 + hh * 8 - vshift;  // accumulator column -> head-dim column
           if (cc >= 0 && cc < p.head_dim) {
-            *reinterpret_cast<uint4*>(o_row + cc) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
-            if constexpr (kDual)
-              *reinterpret_cast<uint4*>(to_row + cc) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
+            if constexpr (TR::kStageOut) {
+              // Staging tile in the layout of a TMA box pair: 64 columns with the 128-byte swizzle, then
+              // TAIL columns with the tail's swizzle; 16-byte chunk k of row r sits at chunk k ^ f(r).
+              uint32_t off;
+              if (cc < 64) {
+                off = static_cast<uint32_t>(row * 128 + (((cc >> 3) ^ (row & 7)) << 4));
+              } else {
+                const int ct = (cc - 64) >> 3;
+                const int fx = TAIL == 64 ? (row & 7) : (TAIL == 32 ? ((row >> 1) & 3) : ((row >> 2) & 1));
+                off = static_cast<uint32_t>(TR::kMainBytes + row * (2 * TAIL) + ((ct ^ fx) << 4));
+              }
+              *reinterpret_cast<uint4*>(smem + TR::kRingBytes + off) =
+                  make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
+            } else {
+              *reinterpret_cast<uint4*>(o_row + cc) = make_uint4(po[4 * hh], po[4 * hh + 1], po[4 * hh + 2], po[4 * hh + 3]);
+              if constexpr (kDual)
+                *reinterpret_cast<uint4*>(to_row + cc) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
+            }
           }
         }
       }
       if (grp == 0)
         p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seqlen_q + lq] =
             (m_used + __log2f(l_tot)) * 0.6931471805599453f;
+      if constexpr (TR::kStageOut) {
+        fence_proxy_async_smem();
+        ok = exchange();  // the tile is staged
+        if (!ok) break;
+        if (warp == 2 && lane == 0) {
+          const uint32_t st = s_q + TR::kRingBytes;
+          tma_store_4d(&p.o_main, st, 0, q0, h, b);
+          if constexpr (TAIL > 0) tma_store_4d(&p.o_tail, st + TR::kMainBytes, 64, q0, h, b);
+          tma_store_commit();
+        }
+      }
       // the accumulator reads above must be complete before the next tile's first MMA overwrites O / T
       tc_fence_before_sync();
     }
+    if (TR::kStageOut && warp == 2 && lane == 0) tma_store_wait_all();
     }  // column split
   }
 

@@ -304,8 +304,10 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
     }
   }
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  if (pair) {
+  if (pair || !dual) {  // kernels that write their outputs with TMA stores
     if ((st = make_map_pair(&p.o_main, &p.o_tail, a->o, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
+  }
+  if (pair) {
     if ((st = make_map_pair(&p.to_main, &p.to_tail, a->to, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
     p.align_enable[1] = 0;  // the pair kernel's V column order has no room for the 8-column shift
     p.num_tiles /= 2;       // tile pairs
