@@ -33,6 +33,8 @@ struct BwdParams {
   // resident / streamed operand maps, "main" = columns [0,64), "tail" = [64, 64+TAIL)
   CUtensorMap r0_main, r0_tail, r1_main, r1_tail;  // DQ: Q, dO      DKV: K, V
   CUtensorMap x0_main, x0_tail, x1_main, x1_tail;  // DQ: K, V       DKV: Q, dO
+  // role-split kernel: the forward output as a TMA load map (DQ mode), the outputs as TMA store maps
+  CUtensorMap o_main, o_tail, out0_main, out0_tail, out1_main, out1_tail;
   // DQ mode: rows of o and dout for delta, lse; outputs
   const void* o;
   const void* dout;

@@ -13,6 +13,7 @@
 #include <cstring>
 
 #include "attn_bwd.cuh"
+#include "attn_bwd_split.cuh"
 #include "attn_fwd.cuh"
 #include "attn_fwd_pair.cuh"
 
@@ -359,8 +360,38 @@ int launch_bwd_inst(const BwdParams& p, int grid, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
 }
 
+// head_dim <= 96: the role-split kernel (P warps / D warps, three ring stages)
+template <typename T, int TAIL, int kMode>
+int launch_bwd_split_inst(const BwdParams& p, int grid, cudaStream_t stream) {
+  using TR = BwdSplitTraits<TAIL>;
+  auto kernel = attn_bwd_split_kernel<T, TAIL, kMode>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::kSmemBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_LAUNCH;
+  }
+  kernel<<<grid, kBwdSplitThreads, TR::kSmemBytes, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
+}
+
+// DMF_ATTN_BWD_SPLIT=0 in the environment keeps the single-warpgroup kernel (for comparisons).
+bool bwd_split_enabled() {
+  static const bool enabled = [] {
+    const char* e = std::getenv("DMF_ATTN_BWD_SPLIT");
+    return e == nullptr || e[0] != '0';
+  }();
+  return enabled;
+}
+
 template <typename T, int kMode>
 int launch_bwd_tail(const BwdParams& p, int tail, int grid, cudaStream_t stream) {
+  if (tail <= 32 && bwd_split_enabled()) {
+    switch (tail) {
+      case 0: return launch_bwd_split_inst<T, 0, kMode>(p, grid, stream);
+      case 16: return launch_bwd_split_inst<T, 16, kMode>(p, grid, stream);
+      case 32: return launch_bwd_split_inst<T, 32, kMode>(p, grid, stream);
+      default: return DMF_ATTN_ERR_HEAD_DIM;
+    }
+  }
   switch (tail) {
     case 0: return launch_bwd_inst<T, 0, kMode>(p, grid, stream);
     case 16: return launch_bwd_inst<T, 16, kMode>(p, grid, stream);
@@ -397,6 +428,10 @@ int run_bwd(const dmf_attn_bwd_args* a) {
   if ((st = make_map_pair(&p.x0_main, &p.x0_tail, a->k, dt, B, Lk, H, D, tail, 128)) != DMF_ATTN_OK) return st;
   if ((st = make_map_pair(&p.x1_main, &p.x1_tail, a->v, dt, B, Lk, H, D, tail, 128)) != DMF_ATTN_OK) return st;
   p.out0 = a->dq.ptr; p.out0_sb = a->dq.stride_b; p.out0_sl = a->dq.stride_l; p.out0_sh = a->dq.stride_h;
+  if (tail <= 32) {  // the role-split kernel loads o and stores its outputs through TMA
+    if ((st = make_map_pair(&p.o_main, &p.o_tail, a->o, dt, B, Lq, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+    if ((st = make_map_pair(&p.out0_main, &p.out0_tail, a->dq, dt, B, Lq, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  }
   p.tiles_per_bh = Lq / 128;
   p.num_tiles = B * H * p.tiles_per_bh;
   p.inner_blocks = Lk / 128;
@@ -411,6 +446,10 @@ int run_bwd(const dmf_attn_bwd_args* a) {
   p2.x0_main = p.r0_main; p2.x0_tail = p.r0_tail; p2.x1_main = p.r1_main; p2.x1_tail = p.r1_tail;
   p2.out0 = a->dk.ptr; p2.out0_sb = a->dk.stride_b; p2.out0_sl = a->dk.stride_l; p2.out0_sh = a->dk.stride_h;
   p2.out1 = a->dv.ptr; p2.out1_sb = a->dv.stride_b; p2.out1_sl = a->dv.stride_l; p2.out1_sh = a->dv.stride_h;
+  if (tail <= 32) {
+    if ((st = make_map_pair(&p2.out0_main, &p2.out0_tail, a->dk, dt, B, Lk, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+    if ((st = make_map_pair(&p2.out1_main, &p2.out1_tail, a->dv, dt, B, Lk, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  }
   p2.tiles_per_bh = Lk / 128;
   p2.num_tiles = B * H * p2.tiles_per_bh;
   p2.inner_blocks = Lq / 128;
