@@ -40,7 +40,8 @@ struct BwdSplitTraits {
   static constexpr bool kOwnOTile = TAIL < 32;
   static constexpr int kTileSmem = kRingBytes + kTileBytes * (kOwnOTile ? 2 : 1);
   static constexpr int kBarRFull = 0, kBarREmpty = 1, kBarSFull = 2, kBarDFull = 3, kBarPFull = 4, kBarGFull = 5,
-                       kBarSEmpty = 6, kBarPEmpty = 7, kBarAccEmpty = 8, kBarOFull = 9, kBarOEmpty = 10, kBarXFull = 11,
+                       kBarSEmpty = 6, kBarPEmpty = 7, kBarAccEmpty = 8, kBarOFull = 9, kBarOEmpty = 10, kBarDEmpty = 11,
+                       kBarXFull = 12,
                        kBarXEmpty = kBarXFull + kStages, kNumBars = kBarXEmpty + kStages;
   static constexpr int kSmemBytes = 1024 + kTileSmem + kStages * kVecBytes + kNumBars * 8 + 16;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
@@ -81,7 +82,8 @@ attn_bwd_split_kernel(const __grid_constant__ BwdParams p) {
     *abort_flag = 0;
     for (int i = 0; i < TR::kNumBars; ++i) {
       uint32_t count = 1;  // TMA transaction or tcgen05.commit
-      if (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarSEmpty || i == TR::kBarAccEmpty)
+      if (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarSEmpty || i == TR::kBarAccEmpty ||
+          i == TR::kBarDEmpty)
         count = 4;                                       // one arrival per warp of a group
       if (i == TR::kBarOEmpty && TR::kOwnOTile) count = 4;  // the D warps have read o (else: one thread, after the stores)
       if (i == TR::kBarPEmpty) count = kDKV ? 5u : 4u;   // the D warps (+ the commit behind dV += P^T dO)
@@ -204,15 +206,30 @@ attn_bwd_split_kernel(const __grid_constant__ BwdParams p) {
           issue_pv<TAIL, TR>(leader, t_a1, t_p, xt + TR::kTileBytes, idesc_pv_main, idesc_pv_tail, j > 0);
           commit(TR::kBarPEmpty);
         }
-        ok = wait(TR::kBarGFull, g & 1u);
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_pv<TAIL, TR>(leader, t_a0, t_d, xt, idesc_pv_main, idesc_pv_tail, j > 0);  // dQ += dS K  /  dK += dS^T Q
-        commit(TR::kBarXEmpty + g % TR::kStages);  // slot free, and "accumulators hold block g" for the D warps
-        if (j + 1 < J) {  // dP of the next block (its streamed tiles were awaited for S)
+        // dP of the next block (its streamed tiles were awaited for S).  In the dQ pass dS has columns of
+        // its own (there is only one accumulator), so dP can be overwritten as soon as the D warps hold it
+        // in registers and is computed while they work; in the dK/dV pass dS lives in the dP columns and
+        // the next dP has to follow the product that reads it.
+        auto issue_next_dp = [&]() {
           issue_qk<TAIL, TR>(leader, t_d, s_r + TR::kTileBytes, x_addr(g + 1u) + TR::kTileBytes, idesc_qk, false);
           commit(TR::kBarDFull);
           if (j + 2 == J) commit(TR::kBarREmpty);
+        };
+        if constexpr (!kDKV) {
+          if (j + 1 < J) {
+            ok = wait(TR::kBarDEmpty, g & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_next_dp();
+          }
+        }
+        ok = wait(TR::kBarGFull, g & 1u);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_pv<TAIL, TR>(leader, t_a0, kDKV ? t_d : t_a1, xt, idesc_pv_main, idesc_pv_tail, j > 0);  // dQ += dS K  /  dK += dS^T Q
+        commit(TR::kBarXEmpty + g % TR::kStages);  // slot free, and "accumulators hold block g" for the D warps
+        if constexpr (kDKV) {
+          if (j + 1 < J) issue_next_dp();
         }
         if (j + 2 < J) {
           ok = issue_s(g + 2u);
@@ -335,41 +352,80 @@ attn_bwd_split_kernel(const __grid_constant__ BwdParams p) {
           tc_fence_before_sync();
           mbar_arrive_warp(bar(TR::kBarPFull));
         } else {
-          // ---- dS = P * (dP - delta), 16-bit, over the dP columns ------------------
-          ok = wait(TR::kBarPFull, gblk & 1u);
-          if (!ok) break;
-          tc_fence_after_sync();
-          uint32_t pp[4][16];
+          // ---- dS = P * (dP - delta), 16-bit ------------------------------------------
+          if constexpr (kDKV) {
+            // over the dP columns (no tensor-memory columns to spare): P first, then dP chunk by chunk
+            ok = wait(TR::kBarPFull, gblk & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t pp[4][16];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_ld_x16(t_p + c * 16, pp[c]);
-          tmem_wait_ld();
-          tc_fence_before_sync();
-          mbar_arrive_warp(bar(TR::kBarPEmpty));  // P has been read
-          ok = wait(TR::kBarDFull, gblk & 1u);
-          if (!ok) break;
-          tc_fence_after_sync();
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t d[32];
-            tmem_ld_x32(t_d + c * 32, d);
+            for (int c = 0; c < 4; ++c) tmem_ld_x16(t_p + c * 16, pp[c]);
             tmem_wait_ld();
-            uint32_t pk[16];
+            tc_fence_before_sync();
+            mbar_arrive_warp(bar(TR::kBarPEmpty));  // P has been read
+            ok = wait(TR::kBarDFull, gblk & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-              float e0 = delta, e1 = delta, e2 = delta, e3 = delta;
-              if constexpr (kDKV) {
+            for (int c = 0; c < 4; ++c) {
+              uint32_t d[32];
+              tmem_ld_x32(t_d + c * 32, d);
+              tmem_wait_ld();
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; i += 2) {
                 const float4 dv = *reinterpret_cast<const float4*>(vstage + 128 + c * 32 + 2 * i);
-                e0 = dv.x; e1 = dv.y; e2 = dv.z; e3 = dv.w;
+                const float2 pa = unpack2<T>(pp[c][i]), pb = unpack2<T>(pp[c][i + 1]);
+                const float g0 = pa.x * (__uint_as_float(d[2 * i]) - dv.x);
+                const float g1 = pa.y * (__uint_as_float(d[2 * i + 1]) - dv.y);
+                const float g2 = pb.x * (__uint_as_float(d[2 * i + 2]) - dv.z);
+                const float g3 = pb.y * (__uint_as_float(d[2 * i + 3]) - dv.w);
+                pk[i] = Pack2<T>::pack(g0, g1);
+                pk[i + 1] = Pack2<T>::pack(g2, g3);
               }
-              const float2 pa = unpack2<T>(pp[c][i]), pb = unpack2<T>(pp[c][i + 1]);
-              const float g0 = pa.x * (__uint_as_float(d[2 * i]) - e0);
-              const float g1 = pa.y * (__uint_as_float(d[2 * i + 1]) - e1);
-              const float g2 = pb.x * (__uint_as_float(d[2 * i + 2]) - e2);
-              const float g3 = pb.y * (__uint_as_float(d[2 * i + 3]) - e3);
-              pk[i] = Pack2<T>::pack(g0, g1);
-              pk[i + 1] = Pack2<T>::pack(g2, g3);
+              tmem_st_x16(t_d + c * 16, pk);  // over dP columns this thread has already read
             }
-            tmem_st_x16(t_d + c * 16, pk);  // over dP columns this thread has already read
+          } else {
+            // into columns of its own (the second accumulator's, unused in this pass): all of dP goes to
+            // registers first and is handed back, so that the next dP is computed during this block's work
+            ok = wait(TR::kBarDFull, gblk & 1u);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t d[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_x32(t_d + c * 32, d[c]);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive_warp(bar(TR::kBarDEmpty));  // dP is in registers
+            ok = wait(TR::kBarPFull, gblk & 1u);
+            if (!ok) break;
+            if (gblk > 0) {  // the product that read the previous dS is complete (its commit freed the ring slot)
+              ok = wait(TR::kBarXEmpty + (gblk - 1u) % TR::kStages, ((gblk - 1u) / TR::kStages) & 1u);
+              if (!ok) break;
+            }
+            tc_fence_after_sync();
+            const uint32_t t_ds = tmem + lane_base + TR::kColAcc1;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pc[16];
+              tmem_ld_x16(t_p + c * 16, pc);
+              tmem_wait_ld();
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; i += 2) {
+                const float2 pa = unpack2<T>(pc[i]), pb = unpack2<T>(pc[i + 1]);
+                const float g0 = pa.x * (__uint_as_float(d[c][2 * i]) - delta);
+                const float g1 = pa.y * (__uint_as_float(d[c][2 * i + 1]) - delta);
+                const float g2 = pb.x * (__uint_as_float(d[c][2 * i + 2]) - delta);
+                const float g3 = pb.y * (__uint_as_float(d[c][2 * i + 3]) - delta);
+                pk[i] = Pack2<T>::pack(g0, g1);
+                pk[i + 1] = Pack2<T>::pack(g2, g3);
+              }
+              tmem_st_x16(t_ds + c * 16, pk);
+            }
+            tc_fence_before_sync();
+            mbar_arrive_warp(bar(TR::kBarPEmpty));  // P has been read
           }
           tmem_wait_st();
           tc_fence_before_sync();
