@@ -18,14 +18,19 @@ def status_word(device):
     return torch.zeros(1, dtype=torch.int32, device=device)
 
 
-def fwd(q, k, v, tq=None, tk=None, tv=None, scale=None, expect=0):
-    """dmf_attn_fwd_dual if tangents are given, else dmf_attn_fwd.  Returns (o, to, lse, status)."""
+def fwd(q, k, v, tq=None, tk=None, tv=None, scale=None, expect=0, packed_out=False):
+    """dmf_attn_fwd_dual if tangents are given, else dmf_attn_fwd.  Returns (o, to, lse, status).
+    packed_out: o and to are the two strided halves of one (B, L, 2, H, D) buffer."""
     dual = tq is not None
     B, Lq, H, D = q.shape
     dev = q.device
     nan = float("nan")
-    o = torch.full((B, Lq, H, D), nan, dtype=q.dtype, device=dev)
-    to = torch.full((B, Lq, H, D), nan, dtype=q.dtype, device=dev) if dual else None
+    if packed_out:
+        both = torch.full((B, Lq, 2, H, D), nan, dtype=q.dtype, device=dev)
+        o, to = both[:, :, 0], (both[:, :, 1] if dual else None)
+    else:
+        o = torch.full((B, Lq, H, D), nan, dtype=q.dtype, device=dev)
+        to = torch.full((B, Lq, H, D), nan, dtype=q.dtype, device=dev) if dual else None
     lse = torch.full((B, H, Lq), nan, dtype=torch.float32, device=dev)
     sw = status_word(dev)
     a = _lib.FwdArgs()
@@ -48,14 +53,20 @@ def fwd(q, k, v, tq=None, tk=None, tv=None, scale=None, expect=0):
     return o, to, lse, st
 
 
-def bwd(dout, q, k, v, o, lse, scale=None, expect=0):
-    """dmf_attn_bwd.  Returns (dq, dk, dv, status)."""
+def bwd(dout, q, k, v, o, lse, scale=None, expect=0, packed_out=False):
+    """dmf_attn_bwd.  Returns (dq, dk, dv, status).
+    packed_out (self-attention shapes only): dq, dk, dv are strided views of one (B, L, 3, H, D) buffer."""
     B, Lq, H, D = q.shape
     dev = q.device
     nan = float("nan")
-    dq = torch.full(q.shape, nan, dtype=q.dtype, device=dev)
-    dk = torch.full(k.shape, nan, dtype=q.dtype, device=dev)
-    dv = torch.full(v.shape, nan, dtype=q.dtype, device=dev)
+    if packed_out:
+        assert q.shape == k.shape
+        grads = torch.full((B, Lq, 3, H, D), nan, dtype=q.dtype, device=dev)
+        dq, dk, dv = grads[:, :, 0], grads[:, :, 1], grads[:, :, 2]
+    else:
+        dq = torch.full(q.shape, nan, dtype=q.dtype, device=dev)
+        dk = torch.full(k.shape, nan, dtype=q.dtype, device=dev)
+        dv = torch.full(v.shape, nan, dtype=q.dtype, device=dev)
     lib = _lib.load()
     nbytes = lib.dmf_attn_bwd_workspace_bytes(B, Lq, k.shape[1], H, D)
     ws = torch.full((max(nbytes, 16),), 0xFF, dtype=torch.uint8, device=dev)  # garbage on purpose

@@ -54,6 +54,19 @@ def test_backward_strided_and_cross_lengths():
     _check((dq, dk, dv), orc.attn_bwd_closed_form(q.float(), k.float(), v.float(), dout.float()))
 
 
+@pytest.mark.parametrize("D", [72, 128])
+def test_backward_strided_outputs(D):
+    """dq, dk, dv as strided views of one (B, L, 3, H, D) gradient buffer, and a strided o / dout as input:
+    bit-identical to the contiguous call."""
+    q, k, v, _, _, _, dout = (x.bfloat16().to(DEV) for x in orc.make_inputs(2, 256, 3, D, seed=5, n_extra=1))
+    o, _, lse, _ = _cabi.fwd(q, k, v)
+    dq0, dk0, dv0, _ = _cabi.bwd(dout, q, k, v, o, lse)
+    od = torch.stack([o, dout], dim=2)  # o and dout as the strided halves of one buffer
+    dq1, dk1, dv1, _ = _cabi.bwd(od[:, :, 1], q, k, v, od[:, :, 0], lse, packed_out=True)
+    assert not dq1.is_contiguous()
+    assert torch.equal(dq0, dq1) and torch.equal(dk0, dk1) and torch.equal(dv0, dv1)
+
+
 def test_backward_many_tiles_and_determinism():
     q, k, v, _, _, _, dout = (x.bfloat16() for x in orc.make_inputs(40, 256, 12, 64, seed=9, n_extra=1))
     _, _, dq, dk, dv = _fwd_bwd((q, k, v), dout)
