@@ -32,13 +32,6 @@
 
 namespace dmf {
 
-#ifndef DMF_PAIR_VSTAGES16
-#define DMF_PAIR_VSTAGES16 3
-#endif
-#ifndef DMF_PAIR_OUTBUFS16
-#define DMF_PAIR_OUTBUFS16 1
-#endif
-
 template <int TAIL>
 struct PairTraits {
   static_assert(TAIL == 0 || TAIL == 16 || TAIL == 32, "the pair kernel needs P in its own tensor-memory columns");
@@ -60,18 +53,22 @@ struct PairTraits {
   static constexpr int kVAtomBytes = 128 * 64;
   static constexpr int kVTileBytes = kVAtoms * kVAtomBytes;
   static constexpr int kVGroupBytes = 2 * kVTileBytes;
-  // Ring depths and output staging (one tile-shaped buffer each for o and to, or one shared by both)
-  // are what fits in 227 KB: head_dim 96 has room for two V stages and one staging buffer only.
+  // Ring depths, output staging (one tile-shaped buffer each for o and to, or one shared by both) and
+  // the number of query-tile buffers are what fits in 227 KB: head_dim 96 has room for two V stages
+  // only; head_dim 64 has room for a second Q/dQ buffer, so that the query tiles of the next pair are
+  // loaded a whole pair ahead (with one buffer that load can only start when the pair's last dS product
+  // has run, and the tensor pipe waits for it: about 3400 cycles per pair).
   static constexpr int kStagesK = 3;
-  static constexpr int kStagesV = TAIL == 32 ? 2 : (TAIL == 16 ? DMF_PAIR_VSTAGES16 : 3);
-  static constexpr int kOutBufs = TAIL == 32 ? 1 : (TAIL == 16 ? DMF_PAIR_OUTBUFS16 : 2);
-  static constexpr int kRingBytes = kQGroupBytes + kStagesK * kKGroupBytes + kStagesV * kVGroupBytes;
+  static constexpr int kStagesV = TAIL == 32 ? 2 : 3;
+  static constexpr int kOutBufs = TAIL == 0 ? 2 : 1;
+  static constexpr int kQBufs = TAIL == 0 ? 2 : 1;
+  static constexpr int kRingBytes = kQBufs * kQGroupBytes + kStagesK * kKGroupBytes + kStagesV * kVGroupBytes;
   static constexpr int kTileSmem = kRingBytes + kOutBufs * kTileBytes;
   static constexpr int kXchgBytes = 4096;
   // barriers
-  static constexpr int kBarQFull = 0, kBarQEmpty = 1, kBarSFull = 2, kBarDSFull = 3, kBarPFull = 4, kBarGFull = 5,
-                       kBarAccFull = 6, kBarXchg = 7, kBarSEmpty = 8, kBarPEmpty = 9, kBarPG = 10, kBarAccEmpty = 11,
-                       kBarKFull = 12,
+  static constexpr int kBarQFull = 0 /* one per Q buffer */, kBarQEmpty = 2 /* one per Q buffer */, kBarSFull = 4,
+                       kBarPFull = 5, kBarGFull = 6, kBarXchg = 7, kBarSEmpty = 8, kBarPEmpty = 9, kBarPG = 10,
+                       kBarAccEmpty = 11, kBarKFull = 12,
                        kBarKEmpty = kBarKFull + kStagesK, kBarVFull = kBarKEmpty + kStagesK,
                        kBarVEmpty = kBarVFull + kStagesV, kNumBars = kBarVEmpty + kStagesV;
   static constexpr int kSmemBytes = 1024 + kTileSmem + kXchgBytes + kNumBars * 8 + 16;
@@ -139,7 +136,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const uint32_t s_q = smem_u32(smem);
-  const uint32_t s_k = s_q + TR::kQGroupBytes;
+  const uint32_t s_k = s_q + TR::kQBufs * TR::kQGroupBytes;
   const uint32_t s_v = s_k + TR::kStagesK * TR::kKGroupBytes;
   uint8_t* out_stage = smem + TR::kRingBytes;  // tile-shaped staging for the TMA stores of o and to
   float* xchg = reinterpret_cast<float*>(smem + TR::kTileSmem);
@@ -161,7 +158,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
     *abort_flag = 0;
     for (int i = 0; i < TR::kNumBars; ++i) {
       uint32_t count = 1;  // tcgen05.commit (multicast from the leader)
-      if (i == TR::kBarQFull || (i >= TR::kBarKFull && i < TR::kBarKEmpty) || (i >= TR::kBarVFull && i < TR::kBarVEmpty))
+      if (i == TR::kBarQFull || i == TR::kBarQFull + 1 || (i >= TR::kBarKFull && i < TR::kBarKEmpty) || (i >= TR::kBarVFull && i < TR::kBarVEmpty))
         count = 2;  // one producer arrival (+ its transaction bytes) per CTA
       if (i == TR::kBarPFull || i == TR::kBarGFull || i == TR::kBarSEmpty || i == TR::kBarAccEmpty)
         count = 8;                         // 4 warps of each CTA
@@ -194,21 +191,32 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
       auto wait = [&](int b_, uint32_t parity) -> bool {
         return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleProducer + b_);
       };
+      // Q and dQ tile of pair number pp_ (the t-th pair of this cluster) into query buffer t % kQBufs
+      auto load_q = [&](int pp_, uint32_t t) -> bool {
+        const int bh_ = pp_ / pairs_per_bh;
+        const int q0 = (2 * (pp_ % pairs_per_bh) + static_cast<int>(rank)) * kBlockQ;
+        const int b_ = bh_ / p.heads, h_ = bh_ % p.heads;
+        const int x_ = -column_shift(p, 0, b_, h_);
+        const uint32_t qb = t % TR::kQBufs, dst = s_q + qb * TR::kQGroupBytes;
+        if (!wait(TR::kBarQEmpty + qb, ((t / TR::kQBufs) & 1u) ^ 1u)) return false;
+        const uint32_t qf = lbar(TR::kBarQFull + qb);
+        mbar_arrive_expect_tx_cluster(qf, TR::kQGroupBytes);
+        tma_load_4d_pair(dst, &p.q_main, qf, x_, q0, h_, b_);
+        tma_load_4d_pair(dst + TR::kTileBytes, &p.tq_main, qf, x_, q0, h_, b_);
+        if constexpr (TAIL > 0) {
+          tma_load_4d_pair(dst + TR::kMainBytes, &p.q_tail, qf, 64 + x_, q0, h_, b_);
+          tma_load_4d_pair(dst + TR::kTileBytes + TR::kMainBytes, &p.tq_tail, qf, 64 + x_, q0, h_, b_);
+        }
+        return true;
+      };
       for (int pp = cluster_id; ok && pp < p.num_tiles; pp += num_clusters, ++tcnt) {
         const int bh = pp / pairs_per_bh;
-        const int q0 = (2 * (pp % pairs_per_bh) + static_cast<int>(rank)) * kBlockQ;
         const int b = bh / p.heads, h = bh % p.heads;
         const int xqk = -column_shift(p, 0, b, h);
-        ok = wait(TR::kBarQEmpty, (tcnt & 1u) ^ 1u);
+        if (tcnt == 0u || TR::kQBufs == 1) ok = load_q(pp, tcnt);
         if (!ok) break;
-        const uint32_t qf = lbar(TR::kBarQFull);
-        mbar_arrive_expect_tx_cluster(qf, TR::kQGroupBytes);
-        tma_load_4d_pair(s_q, &p.q_main, qf, xqk, q0, h, b);
-        tma_load_4d_pair(s_q + TR::kTileBytes, &p.tq_main, qf, xqk, q0, h, b);
-        if constexpr (TAIL > 0) {
-          tma_load_4d_pair(s_q + TR::kMainBytes, &p.q_tail, qf, 64 + xqk, q0, h, b);
-          tma_load_4d_pair(s_q + TR::kTileBytes + TR::kMainBytes, &p.tq_tail, qf, 64 + xqk, q0, h, b);
-        }
+        if (TR::kQBufs == 2 && pp + num_clusters < p.num_tiles) ok = load_q(pp + num_clusters, tcnt + 1u);
+        if (!ok) break;
         for (int j = 0; j < num_kv_blocks; ++j) {
           const int kv0 = j * kBlockKV;
           {
@@ -263,7 +271,8 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
         return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleMma + b_);
       };
       for (int pp = cluster_id; ok && pp < p.num_tiles; pp += num_clusters, ++tcnt) {
-        ok = wait(TR::kBarQFull, tcnt & 1u);
+        const uint32_t qb = tcnt % TR::kQBufs, q_tile = s_q + qb * TR::kQGroupBytes;
+        ok = wait(TR::kBarQFull + qb, (tcnt / TR::kQBufs) & 1u);
         if (!ok) break;
         uint32_t sk = 0, kt = 0;
         // S of the next block: needs the softmax of BOTH CTAs to have read the current S, and the K halves
@@ -273,7 +282,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           if (!wait(TR::kBarKFull + sk, (kcnt / TR::kStagesK) & 1u)) return false;
           tc_fence_after_sync();
           kt = s_k + sk * TR::kKGroupBytes;
-          issue_qk_pair<TAIL, TR>(leader, t_s, s_q, kt, idesc_qk, false);
+          issue_qk_pair<TAIL, TR>(leader, t_s, q_tile, kt, idesc_qk, false);
           commit(TR::kBarSFull);
           ++scnt;
           ++kcnt;
@@ -288,10 +297,10 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
         if (!ok) break;
         ds_sk = sk; ds_kt = kt;
         {
-          issue_qk_pair<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, ds_kt, idesc_qk, false);   // dS_0
-          issue_qk_pair<TAIL, TR>(leader, t_ds, s_q, ds_kt + TR::kKTileBytes, idesc_qk, true);
+          issue_qk_pair<TAIL, TR>(leader, t_ds, q_tile + TR::kTileBytes, ds_kt, idesc_qk, false);   // dS_0
+          issue_qk_pair<TAIL, TR>(leader, t_ds, q_tile, ds_kt + TR::kKTileBytes, idesc_qk, true);
           commit(TR::kBarKEmpty + ds_sk);  // "dS ready" for the G warps and "K slot free" in one
-          if (num_kv_blocks == 1) commit(TR::kBarQEmpty);
+          if (num_kv_blocks == 1) commit(TR::kBarQEmpty + qb);
         }
         if (num_kv_blocks > 1) {
           ok = issue_s();                    // S_1
@@ -329,10 +338,10 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           commit(TR::kBarVEmpty + sv);  // "accumulators up to date" for the softmax warps and "V slot free" in one
           ++vcnt;
           if (j + 1 < num_kv_blocks) {       // dS_{j+1}, on the K block S_{j+1} used
-            issue_qk_pair<TAIL, TR>(leader, t_ds, s_q + TR::kTileBytes, ds_kt, idesc_qk, false);
-            issue_qk_pair<TAIL, TR>(leader, t_ds, s_q, ds_kt + TR::kKTileBytes, idesc_qk, true);
+            issue_qk_pair<TAIL, TR>(leader, t_ds, q_tile + TR::kTileBytes, ds_kt, idesc_qk, false);
+            issue_qk_pair<TAIL, TR>(leader, t_ds, q_tile, ds_kt + TR::kKTileBytes, idesc_qk, true);
             commit(TR::kBarKEmpty + ds_sk);
-            if (j + 2 == num_kv_blocks) commit(TR::kBarQEmpty);
+            if (j + 2 == num_kv_blocks) commit(TR::kBarQEmpty + qb);
           }
           ds_sk = nx_sk; ds_kt = nx_kt;
         }
