@@ -67,13 +67,13 @@ def _peaks():
 def _kernel_name(op, D, L):
     """Name of the kernel instance the library picks for this shape (same rule as the launcher)."""
     tail = ((D + 15) // 16) * 16 - 64
-    if op == "dual":
+    if op in ("dual", "fwd"):
+        kind = "dual" if op == "dual" else "plain"
         pair = tail <= 32 and (L // 128) % 2 == 0 and os.environ.get("DMF_ATTN_PAIR", "1") != "0"
-        return (f"attn_fwd_pair_kernel<bf16, TAIL={tail}> (cta_group::2 cluster pair)" if pair
-                else f"attn_fwd_kernel<bf16, TAIL={tail}, dual>")
-    if op == "fwd":
-        return f"attn_fwd_kernel<bf16, TAIL={tail}, plain>"
-    return f"attn_bwd_kernel<bf16, TAIL={tail}, dQ> + attn_bwd_kernel<bf16, TAIL={tail}, dK/dV>"
+        return (f"attn_fwd_pair_kernel<bf16, TAIL={tail}, {kind}> (cta_group::2 cluster pair)" if pair
+                else f"attn_fwd_kernel<bf16, TAIL={tail}, {kind}>")
+    name = "attn_bwd_split_kernel" if tail <= 32 and os.environ.get("DMF_ATTN_BWD_SPLIT", "1") != "0" else "attn_bwd_kernel"
+    return f"{name}<bf16, TAIL={tail}, dQ> + {name}<bf16, TAIL={tail}, dK/dV>"
 
 
 def _traffic(workload):

@@ -125,7 +125,11 @@ __device__ __forceinline__ void issue_pv_pair(bool leader, uint32_t d_tmem, uint
 // ---- the kernel ---------------------------------------------------------------
 // p.k_* maps have a box of 64 rows; p.num_tiles counts tile PAIRS; p.num_q_tiles is even.
 
-template <typename T, int TAIL>
+// kDual = false is the plain forward on the same skeleton: no tangent tiles are loaded, no dS / P dV / G V
+// products are issued, the G warps only do the epilogue.  Each softmax warp then has its scheduler to
+// itself and a whole score row per thread (no row-max exchange between warpgroups as in the
+// single-CTA plain forward).
+template <typename T, int TAIL, bool kDual>
 __global__ void __launch_bounds__(kPairThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
   using TR = PairTraits<TAIL>;
@@ -164,7 +168,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
         count = 8;                         // 4 warps of each CTA
       if (i == TR::kBarXchg) count = 4;    // the 4 local P warps
       if (i == TR::kBarPG) count = 4;      // the 4 local P warps
-      if (i == TR::kBarPEmpty) count = 5;  // commit + the 4 local G warps
+      if (i == TR::kBarPEmpty) count = kDual ? 5 : 1;  // commit (+ the 4 local G warps, which read P too)
       mbar_init(bar(i), count);
     }
     fence_mbar_init();
@@ -200,12 +204,13 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
         const uint32_t qb = t % TR::kQBufs, dst = s_q + qb * TR::kQGroupBytes;
         if (!wait(TR::kBarQEmpty + qb, ((t / TR::kQBufs) & 1u) ^ 1u)) return false;
         const uint32_t qf = lbar(TR::kBarQFull + qb);
-        mbar_arrive_expect_tx_cluster(qf, TR::kQGroupBytes);
+        mbar_arrive_expect_tx_cluster(qf, kDual ? TR::kQGroupBytes : TR::kTileBytes);
         tma_load_4d_pair(dst, &p.q_main, qf, x_, q0, h_, b_);
-        tma_load_4d_pair(dst + TR::kTileBytes, &p.tq_main, qf, x_, q0, h_, b_);
+        if constexpr (kDual) tma_load_4d_pair(dst + TR::kTileBytes, &p.tq_main, qf, x_, q0, h_, b_);
         if constexpr (TAIL > 0) {
           tma_load_4d_pair(dst + TR::kMainBytes, &p.q_tail, qf, 64 + x_, q0, h_, b_);
-          tma_load_4d_pair(dst + TR::kTileBytes + TR::kMainBytes, &p.tq_tail, qf, 64 + x_, q0, h_, b_);
+          if constexpr (kDual)
+            tma_load_4d_pair(dst + TR::kTileBytes + TR::kMainBytes, &p.tq_tail, qf, 64 + x_, q0, h_, b_);
         }
         return true;
       };
@@ -225,12 +230,13 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
             if (!ok) break;
             const uint32_t dst = s_k + s * TR::kKGroupBytes, fb = lbar(TR::kBarKFull + s);
             const int kr = kv0 + 64 * static_cast<int>(rank);  // this CTA's half of the key rows
-            mbar_arrive_expect_tx_cluster(fb, TR::kKGroupBytes);
+            mbar_arrive_expect_tx_cluster(fb, kDual ? TR::kKGroupBytes : TR::kKTileBytes);
             tma_load_4d_pair(dst, &p.k_main, fb, xqk, kr, h, b);
-            tma_load_4d_pair(dst + TR::kKTileBytes, &p.tk_main, fb, xqk, kr, h, b);
+            if constexpr (kDual) tma_load_4d_pair(dst + TR::kKTileBytes, &p.tk_main, fb, xqk, kr, h, b);
             if constexpr (TAIL > 0) {
               tma_load_4d_pair(dst + TR::kKMainBytes, &p.k_tail, fb, 64 + xqk, kr, h, b);
-              tma_load_4d_pair(dst + TR::kKTileBytes + TR::kKMainBytes, &p.tk_tail, fb, 64 + xqk, kr, h, b);
+              if constexpr (kDual)
+                tma_load_4d_pair(dst + TR::kKTileBytes + TR::kKMainBytes, &p.tk_tail, fb, 64 + xqk, kr, h, b);
             }
             ++kcnt;
           }
@@ -239,14 +245,14 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
             ok = wait(TR::kBarVEmpty + s, ph ^ 1u);
             if (!ok) break;
             const uint32_t dst = s_v + s * TR::kVGroupBytes, fb = lbar(TR::kBarVFull + s);
-            mbar_arrive_expect_tx_cluster(fb, TR::kVGroupBytes);
+            mbar_arrive_expect_tx_cluster(fb, kDual ? TR::kVGroupBytes : TR::kVTileBytes);
             const int x0 = 32 * static_cast<int>(rank);                   // columns [32r, 32r+32)
             tma_load_4d_pair(dst, &p.v_map, fb, x0, kv0, h, b);
-            tma_load_4d_pair(dst + TR::kVTileBytes, &p.tv_map, fb, x0, kv0, h, b);
+            if constexpr (kDual) tma_load_4d_pair(dst + TR::kVTileBytes, &p.tv_map, fb, x0, kv0, h, b);
             if constexpr (TR::kVAtoms > 1) {
               const int x1 = 64 + TR::kExtra * static_cast<int>(rank);    // columns [64 + r e, ...): e of them used
               tma_load_4d_pair(dst + TR::kVAtomBytes, &p.v_map, fb, x1, kv0, h, b);
-              tma_load_4d_pair(dst + TR::kVTileBytes + TR::kVAtomBytes, &p.tv_map, fb, x1, kv0, h, b);
+              if constexpr (kDual) tma_load_4d_pair(dst + TR::kVTileBytes + TR::kVAtomBytes, &p.tv_map, fb, x1, kv0, h, b);
             }
             ++vcnt;
           }
@@ -274,7 +280,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
         const uint32_t qb = tcnt % TR::kQBufs, q_tile = s_q + qb * TR::kQGroupBytes;
         ok = wait(TR::kBarQFull + qb, (tcnt / TR::kQBufs) & 1u);
         if (!ok) break;
-        uint32_t sk = 0, kt = 0;
+        uint32_t sk = 0, kt = 0, s_in_tile = 0;
         // S of the next block: needs the softmax of BOTH CTAs to have read the current S, and the K halves
         auto issue_s = [&]() -> bool {
           sk = kcnt % TR::kStagesK;
@@ -284,6 +290,10 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           kt = s_k + sk * TR::kKGroupBytes;
           issue_qk_pair<TAIL, TR>(leader, t_s, q_tile, kt, idesc_qk, false);
           commit(TR::kBarSFull);
+          if constexpr (!kDual) {  // nothing else reads this K block or, after the pair's last S, its query tile
+            commit(TR::kBarKEmpty + sk);
+            if (++s_in_tile == static_cast<uint32_t>(num_kv_blocks)) commit(TR::kBarQEmpty + qb);
+          }
           ++scnt;
           ++kcnt;
           return true;
@@ -296,7 +306,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
         ok = issue_s();                      // S_0
         if (!ok) break;
         ds_sk = sk; ds_kt = kt;
-        {
+        if constexpr (kDual) {
           issue_qk_pair<TAIL, TR>(leader, t_ds, q_tile + TR::kTileBytes, ds_kt, idesc_qk, false);   // dS_0
           issue_qk_pair<TAIL, TR>(leader, t_ds, q_tile, ds_kt + TR::kKTileBytes, idesc_qk, true);
           commit(TR::kBarKEmpty + ds_sk);  // "dS ready" for the G warps and "K slot free" in one
@@ -321,8 +331,12 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           }
           tc_fence_after_sync();
           issue_pv_pair<TR>(leader, t_o, t_p, vt, idesc_pv, j > 0);                    // O += P V
-          issue_pv_pair<TR>(leader, t_t, t_p, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
-          commit(TR::kBarPEmpty);
+          if constexpr (kDual) {
+            issue_pv_pair<TR>(leader, t_t, t_p, vt + TR::kVTileBytes, idesc_pv, j > 0);  // T += P dV
+            commit(TR::kBarPEmpty);
+          } else {
+            commit(TR::kBarVEmpty + sv);  // plain forward: V slot free, O up to date, P read, all in one
+          }
           uint32_t nx_sk = 0, nx_kt = 0;
           const bool s_ahead = (j + 2 < num_kv_blocks);
           if (s_ahead) {
@@ -330,14 +344,16 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
             if (!ok) break;
             nx_sk = sk; nx_kt = kt;
           }
-          ok = wait(TR::kBarGFull, gcnt & 1u);
-          if (!ok) break;
-          ++gcnt;
-          tc_fence_after_sync();
-          issue_pv_pair<TR>(leader, t_t, t_ds, vt, idesc_pv, true);                    // T += G V
-          commit(TR::kBarVEmpty + sv);  // "accumulators up to date" for the softmax warps and "V slot free" in one
+          if constexpr (kDual) {
+            ok = wait(TR::kBarGFull, gcnt & 1u);
+            if (!ok) break;
+            ++gcnt;
+            tc_fence_after_sync();
+            issue_pv_pair<TR>(leader, t_t, t_ds, vt, idesc_pv, true);                  // T += G V
+          }
+          if constexpr (kDual) commit(TR::kBarVEmpty + sv);  // "accumulators up to date" and "V slot free" in one
           ++vcnt;
-          if (j + 1 < num_kv_blocks) {       // dS_{j+1}, on the K block S_{j+1} used
+          if (kDual && j + 1 < num_kv_blocks) {  // dS_{j+1}, on the K block S_{j+1} used
             issue_qk_pair<TAIL, TR>(leader, t_ds, q_tile + TR::kTileBytes, ds_kt, idesc_qk, false);
             issue_qk_pair<TAIL, TR>(leader, t_ds, q_tile, ds_kt + TR::kKTileBytes, idesc_qk, true);
             commit(TR::kBarKEmpty + ds_sk);
@@ -463,7 +479,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
               l += s0 + s1;
             }
             if (gblk > 0) {  // the P V products of the previous block and the G warps have read P
-              ok = wait(TR::kBarPEmpty, (gblk - 1u) & 1u);
+              ok = kDual ? wait(TR::kBarPEmpty, (gblk - 1u) & 1u) : wait_acc(gblk - 1u);
               if (!ok) break;
               tc_fence_after_sync();
             }
@@ -477,8 +493,8 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive_warp_cluster(lbar(TR::kBarPFull));  // for the MMA warp of the leader
-            mbar_arrive_warp(bar(TR::kBarPG));                // for this CTA's G warps
-          } else {
+            if constexpr (kDual) mbar_arrive_warp(bar(TR::kBarPG));  // for this CTA's G warps
+          } else if constexpr (kDual) {
             // ---- G = P * dS * scale, mu += rowsum(G) ---------------------------
             // P first: it is ready long before dS, and once it sits in registers its columns can be
             // handed back to the P warps (they would otherwise wait for this whole block of G work).
@@ -566,10 +582,11 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           else
             return static_cast<uint32_t>(TR::kMainBytes + row * 32 + ((ct ^ ((row >> 2) & 1)) << 4));
         };
+        constexpr int kPasses = (kDual && TR::kOutBufs == 1) ? 2 : 1;
 #pragma unroll
-        for (int pass = 0; pass < (TR::kOutBufs == 1 ? 2 : 1); ++pass) {
+        for (int pass = 0; pass < kPasses; ++pass) {
           const bool do_o = TR::kOutBufs == 2 || pass == 0;
-          const bool do_t = TR::kOutBufs == 2 || pass == 1;
+          const bool do_t = kDual && (TR::kOutBufs == 2 || pass == 1);
 #pragma unroll
           for (int c = 0; c < DPAD / 16; ++c) {
             uint32_t a[16], t[16];
@@ -597,7 +614,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
                 *reinterpret_cast<uint4*>(st_t + off) = make_uint4(pt[4 * hh], pt[4 * hh + 1], pt[4 * hh + 2], pt[4 * hh + 3]);
             }
           }
-          if (do_t) {  // O and T are in registers / shared memory: the next tile may overwrite them
+          if (pass == kPasses - 1) {  // O and T are in registers / shared memory: the next tile may overwrite them
             tc_fence_before_sync();
             mbar_arrive_warp_cluster(lbar(TR::kBarAccEmpty));
           }
@@ -613,9 +630,9 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
               if constexpr (TAIL > 0) tma_store_4d(&p.to_tail, smem_u32(st_t) + TR::kMainBytes, 64, q0, h, b);
             }
             tma_store_commit();
-            if (TR::kOutBufs == 1 && pass == 0) tma_store_wait_read();
+            if (kPasses == 2 && pass == 0) tma_store_wait_read();
           }
-          if (TR::kOutBufs == 1 && pass == 0) named_bar_sync(1, 128);  // the shared tile is free for T
+          if (kPasses == 2 && pass == 0) named_bar_sync(1, 128);  // the shared tile is free for T
         }
       }
       if (!p_role && warp == 6 && lane == 0) tma_store_wait_all();

@@ -192,10 +192,10 @@ int launch_fwd_tail(const FwdParams& p, int tail, int grid, cudaStream_t stream)
 
 // ---- forward launch, CTA-pair variant (dual pass, head_dim <= 96, even number of query tiles) ----
 
-template <typename T, int TAIL>
+template <typename T, int TAIL, bool kDual>
 int launch_pair_inst(const FwdParams& p, int clusters, cudaStream_t stream) {
   using TR = PairTraits<TAIL>;
-  auto kernel = attn_fwd_pair_kernel<T, TAIL>;
+  auto kernel = attn_fwd_pair_kernel<T, TAIL, kDual>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::kSmemBytes) != cudaSuccess) {
     (void)cudaGetLastError();
     return DMF_ATTN_ERR_LAUNCH;
@@ -226,12 +226,12 @@ int launch_pair_inst(const FwdParams& p, int clusters, cudaStream_t stream) {
   return DMF_ATTN_OK;
 }
 
-template <typename T>
+template <typename T, bool kDual>
 int launch_pair_tail(const FwdParams& p, int tail, int clusters, cudaStream_t stream) {
   switch (tail) {
-    case 0: return launch_pair_inst<T, 0>(p, clusters, stream);
-    case 16: return launch_pair_inst<T, 16>(p, clusters, stream);
-    case 32: return launch_pair_inst<T, 32>(p, clusters, stream);
+    case 0: return launch_pair_inst<T, 0, kDual>(p, clusters, stream);
+    case 16: return launch_pair_inst<T, 16, kDual>(p, clusters, stream);
+    case 32: return launch_pair_inst<T, 32, kDual>(p, clusters, stream);
     default: return DMF_ATTN_ERR_HEAD_DIM;
   }
 }
@@ -257,7 +257,7 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
   const int B = a->batch, H = a->heads, D = a->head_dim, Lq = a->seqlen_q, Lk = a->seqlen_kv, dt = a->dtype;
   if ((st = make_map_pair(&p.q_main, &p.q_tail, a->q, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
   // CTA-pair kernel: dual pass, P in its own tensor-memory columns (head_dim <= 96), tiles pair up
-  const bool pair = dual && tail <= 32 && ((Lq / kBlockQ) % 2 == 0) && pair_kernel_enabled();
+  const bool pair = tail <= 32 && ((Lq / kBlockQ) % 2 == 0) && pair_kernel_enabled();
   const int k_box_rows = pair ? kBlockKV / 2 : kBlockKV;  // a CTA of a pair loads half of the key rows
   if ((st = make_map_pair(&p.k_main, &p.k_tail, a->k, dt, B, Lk, H, D, tail, k_box_rows)) != DMF_ATTN_OK) return st;
   if ((st = make_map(&p.v_map, a->v, dt, B, Lk, H, D, 32, kBlockKV, CU_TENSOR_MAP_SWIZZLE_64B)) != DMF_ATTN_OK) return st;
@@ -309,13 +309,17 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
     if ((st = make_map_pair(&p.o_main, &p.o_tail, a->o, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
   }
   if (pair) {
-    if ((st = make_map_pair(&p.to_main, &p.to_tail, a->to, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
+    if (dual && (st = make_map_pair(&p.to_main, &p.to_tail, a->to, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK)
+      return st;
     p.align_enable[1] = 0;  // the pair kernel's V column order has no room for the 8-column shift
     p.num_tiles /= 2;       // tile pairs
     const int max_clusters = sm_count / 2;
     const int clusters = p.num_tiles < max_clusters ? p.num_tiles : max_clusters;
-    return dt == DMF_ATTN_BF16 ? launch_pair_tail<__nv_bfloat16>(p, tail, clusters, stream)
-                               : launch_pair_tail<__half>(p, tail, clusters, stream);
+    if (dual)
+      return dt == DMF_ATTN_BF16 ? launch_pair_tail<__nv_bfloat16, true>(p, tail, clusters, stream)
+                                 : launch_pair_tail<__half, true>(p, tail, clusters, stream);
+    return dt == DMF_ATTN_BF16 ? launch_pair_tail<__nv_bfloat16, false>(p, tail, clusters, stream)
+                               : launch_pair_tail<__half, false>(p, tail, clusters, stream);
   }
   const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
   if (dt == DMF_ATTN_BF16)
