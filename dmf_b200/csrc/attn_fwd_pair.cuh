@@ -32,7 +32,11 @@
 
 namespace dmf {
 
-template <int TAIL>
+// kShort: key sequences of at most kShortMaxBlocks blocks.  With so few blocks per tile the third V stage
+// buys nothing, while writing the tile out is a large part of a tile's time: the shared memory goes to a
+// second staging tile instead, so that o and to are staged and stored without waiting for the first
+// store to have read its tile (behind the loads queued in the TMA unit that wait takes 2000 cycles).
+template <int TAIL, bool kShort = false>
 struct PairTraits {
   static_assert(TAIL == 0 || TAIL == 16 || TAIL == 32, "the pair kernel needs P in its own tensor-memory columns");
   static constexpr int kDPad = 64 + TAIL;
@@ -59,8 +63,8 @@ struct PairTraits {
   // loaded a whole pair ahead (with one buffer that load can only start when the pair's last dS product
   // has run, and the tensor pipe waits for it: about 3400 cycles per pair).
   static constexpr int kStagesK = 3;
-  static constexpr int kStagesV = TAIL == 32 ? 2 : 3;
-  static constexpr int kOutBufs = TAIL == 0 ? 2 : 1;
+  static constexpr int kStagesV = (TAIL == 32 || kShort) ? 2 : 3;
+  static constexpr int kOutBufs = (TAIL == 0 || (kShort && TAIL == 16)) ? 2 : 1;
   static constexpr int kQBufs = TAIL == 0 ? 2 : 1;
   static constexpr int kRingBytes = kQBufs * kQGroupBytes + kStagesK * kKGroupBytes + kStagesV * kVGroupBytes;
   static constexpr int kTileSmem = kRingBytes + kOutBufs * kTileBytes;
@@ -81,6 +85,7 @@ struct PairTraits {
 };
 
 constexpr int kPairThreads = 320;
+constexpr int kShortMaxBlocks = 2;  // see PairTraits
 
 // head-dim column of accumulator column t (t a multiple of 8); see the header comment
 template <typename TR>
@@ -129,10 +134,10 @@ __device__ __forceinline__ void issue_pv_pair(bool leader, uint32_t d_tmem, uint
 // products are issued, the G warps only do the epilogue.  Each softmax warp then has its scheduler to
 // itself and a whole score row per thread (no row-max exchange between warpgroups as in the
 // single-CTA plain forward).
-template <typename T, int TAIL, bool kDual>
+template <typename T, int TAIL, bool kDual, bool kShort>
 __global__ void __launch_bounds__(kPairThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
-  using TR = PairTraits<TAIL>;
+  using TR = PairTraits<TAIL, kShort>;
   constexpr int DPAD = TR::kDPad;
   constexpr bool kBf16 = Pack2<T>::kIsBf16;
 

@@ -192,10 +192,10 @@ int launch_fwd_tail(const FwdParams& p, int tail, int grid, cudaStream_t stream)
 
 // ---- forward launch, CTA-pair variant (dual pass, head_dim <= 96, even number of query tiles) ----
 
-template <typename T, int TAIL, bool kDual>
+template <typename T, int TAIL, bool kDual, bool kShort>
 int launch_pair_inst(const FwdParams& p, int clusters, cudaStream_t stream) {
-  using TR = PairTraits<TAIL>;
-  auto kernel = attn_fwd_pair_kernel<T, TAIL, kDual>;
+  using TR = PairTraits<TAIL, kShort>;
+  auto kernel = attn_fwd_pair_kernel<T, TAIL, kDual, kShort>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::kSmemBytes) != cudaSuccess) {
     (void)cudaGetLastError();
     return DMF_ATTN_ERR_LAUNCH;
@@ -229,9 +229,11 @@ int launch_pair_inst(const FwdParams& p, int clusters, cudaStream_t stream) {
 template <typename T, bool kDual>
 int launch_pair_tail(const FwdParams& p, int tail, int clusters, cudaStream_t stream) {
   switch (tail) {
-    case 0: return launch_pair_inst<T, 0, kDual>(p, clusters, stream);
-    case 16: return launch_pair_inst<T, 16, kDual>(p, clusters, stream);
-    case 32: return launch_pair_inst<T, 32, kDual>(p, clusters, stream);
+    case 0: return launch_pair_inst<T, 0, kDual, false>(p, clusters, stream);
+    case 16:  // the only head_dim whose shared-memory split depends on the length of the key sequence
+      return p.seqlen_kv <= kShortMaxBlocks * kBlockKV ? launch_pair_inst<T, 16, kDual, true>(p, clusters, stream)
+                                                       : launch_pair_inst<T, 16, kDual, false>(p, clusters, stream);
+    case 32: return launch_pair_inst<T, 32, kDual, false>(p, clusters, stream);
     default: return DMF_ATTN_ERR_HEAD_DIM;
   }
 }
