@@ -45,7 +45,7 @@ CASES = {
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of the reference source tree")
     args = ap.parse_args()
     os.environ.setdefault("TRITON_INTERPRET", "1")
 

@@ -36,7 +36,7 @@ def tiny_inputs():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of the reference source tree")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     for name in ("flash_attn_3", "flash_attn_3._C"):
