@@ -372,6 +372,59 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_rmsnorm(args):
+    """The fused per-head RMS norm of q and k with tangents (one of the callers either side of the attention op):
+    a step normalises q and k of a packed qkv projection of the workload's shape, with their tangents."""
+    import torch
+    from dmf_b200 import ops
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, L, H, D, ts, _, desc = WORKLOADS[args.workload]
+    if args.batch is not None:
+        B = args.batch
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    qkv = torch.randn(B, L, 3, H, D, device=dev, generator=gen).to(torch.bfloat16)
+    tqkv = (torch.randn(B, L, 3, H, D, device=dev, generator=gen) * ts).to(torch.bfloat16)
+    w = torch.ones(D, device=dev)
+
+    def step():
+        ops.rmsnorm_fwd_raw(qkv[:, :, 0], tqkv[:, :, 0], w, 1e-6)
+        return ops.rmsnorm_fwd_raw(qkv[:, :, 1], tqkv[:, :, 1], w, 1e-6)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.active.set()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.active.clear()
+    sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    nbytes = 2 * 4 * B * L * H * D * 2.0  # q and k: read x, tx; write y, ty
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    peaks = _peaks()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "qk_rmsnorm_dual_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload} shapes: per-head RMS norm of q and k with tangents, strided views "
+                                   f"of packed (B={B}, L={L}, 3, H={H}, D={D}) projections",
+                       "l2": "inputs are larger than the 126 MB L2; no flush between steps"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                         "peak_source": f"HBM copy, of {peaks['source']}", "algorithmic_bytes_per_step": nbytes,
+                         "kernel": "rmsnorm_fwd_kernel<bf16, dual> x 2"},
+            "op": "rmsnorm", "gpu_launches": 2 * args.steps, "clocks": sampler.summary()}))
+
+
 def run_model(args):
     """Whole-model configurations: C4 (training step, data parallel with an NCCL gradient
     all-reduce) and C5 (4-step Euler sampling, sharded per rank, no collective)."""
@@ -501,7 +554,7 @@ def main():
                          "global batch 256; C5: DMFT-XL/2 4-step Euler sampling at 512px, 64 images per GPU")
     ap.add_argument("--micro-batch", type=int, default=32, help="C4: images per forward/backward pass")
     ap.add_argument("--model", default="DMFT-XL/2", help="C4/C5: harness model name (smaller ones for smoke runs)")
-    ap.add_argument("--op", choices=["dual", "fwd", "bwd"], default="dual",
+    ap.add_argument("--op", choices=["dual", "fwd", "bwd", "rmsnorm"], default="dual",
                     help="C2/C3: entry point to time (default: the fused forward+tangent, which is the bench line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -518,6 +571,8 @@ def main():
         run_model(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.op == "rmsnorm":
+        run_rmsnorm(args)
     else:
         run_ours(args)
 

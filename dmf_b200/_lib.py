@@ -26,6 +26,7 @@ EXPORTS = (
     "dmf_attn_abi_version", "dmf_attn_status_string", "dmf_attn_fwd_dual", "dmf_attn_fwd",
     "dmf_attn_bwd", "dmf_attn_bwd_static", "dmf_attn_bwd_workspace_bytes", "dmf_attn_check_status_word",
     "dmf_attn_validate_fwd", "dmf_attn_validate_bwd",
+    "dmf_rmsnorm_fwd", "dmf_rmsnorm_bwd", "dmf_rmsnorm_bwd_workspace_bytes",
 )
 
 
@@ -54,6 +55,25 @@ class BwdArgs(C.Structure):
         ("dq", Tensor4), ("dk", Tensor4), ("dv", Tensor4),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status_word", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
+class RmsNormArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("seqlen", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("dtype", C.c_int32), ("eps", C.c_float),
+        ("x", Tensor4), ("tx", Tensor4), ("y", Tensor4), ("ty", Tensor4),
+        ("weight", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
+class RmsNormBwdArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("seqlen", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("dtype", C.c_int32), ("eps", C.c_float),
+        ("dy", Tensor4), ("x", Tensor4), ("dx", Tensor4),
+        ("weight", C.c_void_p), ("dweight", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
     ]
 
 
@@ -100,6 +120,12 @@ def load() -> C.CDLL:
         lib.dmf_attn_validate_fwd.argtypes = [C.POINTER(FwdArgs), C.c_int]
         lib.dmf_attn_validate_bwd.restype = C.c_int
         lib.dmf_attn_validate_bwd.argtypes = [C.POINTER(BwdArgs)]
+        lib.dmf_rmsnorm_fwd.restype = C.c_int
+        lib.dmf_rmsnorm_fwd.argtypes = [C.POINTER(RmsNormArgs)]
+        lib.dmf_rmsnorm_bwd.restype = C.c_int
+        lib.dmf_rmsnorm_bwd.argtypes = [C.POINTER(RmsNormBwdArgs)]
+        lib.dmf_rmsnorm_bwd_workspace_bytes.restype = C.c_size_t
+        lib.dmf_rmsnorm_bwd_workspace_bytes.argtypes = [C.c_int32]
         got = lib.dmf_attn_abi_version()
         if got != ABI_VERSION:
             raise ImportError(f"libdmf_attn.so has ABI version {got}, this package expects {ABI_VERSION}")

@@ -16,6 +16,7 @@
 #include "attn_bwd_split.cuh"
 #include "attn_fwd.cuh"
 #include "attn_fwd_pair.cuh"
+#include "rmsnorm.cuh"
 
 namespace {
 
@@ -515,6 +516,107 @@ int run_bwd_static(const dmf_attn_bwd_args* a) {
   return run_bwd(&local);
 }
 
+// ---- per-head RMS norm (q / k) with tangent, and its backward ----
+
+constexpr int kRmsMaxBlocks = 2048;  // upper bound of the grid, fixes the size of the backward's workspace
+
+int rms_check(int batch, int seqlen, int heads, int d, int dtype) {
+  if (dtype != DMF_ATTN_BF16 && dtype != DMF_ATTN_FP16) return DMF_ATTN_ERR_DTYPE;
+  if (d < 8 || d > 128 || (d % 8) != 0) return DMF_ATTN_ERR_HEAD_DIM;
+  if (batch < 1 || heads < 1 || seqlen < 1) return DMF_ATTN_ERR_SHAPE;
+  if (static_cast<int64_t>(batch) * seqlen * heads >= (int64_t{1} << 31)) return DMF_ATTN_ERR_SHAPE;
+  return DMF_ATTN_OK;
+}
+
+int rms_grid(int64_t rows, int head_dim, int unroll, int sm_count) {
+  const int64_t block_rows = rms_rows_per_block(head_dim / 8, unroll);
+  const int64_t want = (rows + block_rows - 1) / block_rows;
+  int64_t cap = static_cast<int64_t>(sm_count) * 8;  // 8 blocks of 256 threads per SM
+  if (cap > kRmsMaxBlocks) cap = kRmsMaxBlocks;
+  return static_cast<int>(want < cap ? want : cap);
+}
+
+// the kernels are compiled per number of 16-byte chunks in a row (head_dim / 8 = 1..16)
+template <typename T, int C = 16>
+void rms_launch_fwd(int chunks, bool dual, int grid, cudaStream_t stream, const RmsParams& p) {
+  if (chunks == C) {
+    if (dual) rmsnorm_fwd_kernel<T, C, true><<<grid, kRmsThreads, 0, stream>>>(p);
+    else rmsnorm_fwd_kernel<T, C, false><<<grid, kRmsThreads, 0, stream>>>(p);
+  } else if constexpr (C > 1) {
+    rms_launch_fwd<T, C - 1>(chunks, dual, grid, stream, p);
+  }
+}
+
+template <typename T, int C = 16>
+void rms_launch_bwd(int chunks, int grid, cudaStream_t stream, const RmsParams& p) {
+  if (chunks == C) rmsnorm_bwd_kernel<T, C><<<grid, kRmsThreads, 0, stream>>>(p);
+  else if constexpr (C > 1) rms_launch_bwd<T, C - 1>(chunks, grid, stream, p);
+}
+
+int run_rmsnorm_fwd(const dmf_rmsnorm_args* a) {
+  if (a == nullptr || a->weight == nullptr) return DMF_ATTN_ERR_NULL;
+  int st = rms_check(a->batch, a->seqlen, a->heads, a->head_dim, a->dtype);
+  if (st != DMF_ATTN_OK) return st;
+  const bool dual = a->tx.ptr != nullptr;
+  if ((st = check_tensor(a->x, 2)) != DMF_ATTN_OK || (st = check_tensor(a->y, 2)) != DMF_ATTN_OK) return st;
+  if (dual && ((st = check_tensor(a->tx, 2)) != DMF_ATTN_OK || (st = check_tensor(a->ty, 2)) != DMF_ATTN_OK)) return st;
+  int sm_count = 0;
+  if ((st = device_info(&sm_count)) != DMF_ATTN_OK) return st;
+  RmsParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.x = a->x.ptr; p.x_sb = a->x.stride_b; p.x_sl = a->x.stride_l; p.x_sh = a->x.stride_h;
+  p.y = a->y.ptr; p.y_sb = a->y.stride_b; p.y_sl = a->y.stride_l; p.y_sh = a->y.stride_h;
+  if (dual) {
+    p.tx = a->tx.ptr; p.tx_sb = a->tx.stride_b; p.tx_sl = a->tx.stride_l; p.tx_sh = a->tx.stride_h;
+    p.ty = a->ty.ptr; p.ty_sb = a->ty.stride_b; p.ty_sl = a->ty.stride_l; p.ty_sh = a->ty.stride_h;
+  }
+  p.w = a->weight;
+  p.batch = a->batch; p.seqlen = a->seqlen; p.heads = a->heads; p.head_dim = a->head_dim;
+  p.rows = static_cast<int64_t>(a->batch) * a->seqlen * a->heads;
+  p.eps = a->eps;
+  const int grid = rms_grid(p.rows, a->head_dim, rms_unroll_fwd(dual), sm_count);
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (a->dtype == DMF_ATTN_BF16) rms_launch_fwd<__nv_bfloat16>(a->head_dim / 8, dual, grid, stream, p);
+  else rms_launch_fwd<__half>(a->head_dim / 8, dual, grid, stream, p);
+  return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
+}
+
+size_t rmsnorm_bwd_workspace_bytes(int d) {
+  if (d < 8 || d > 128 || (d % 8) != 0) return 0;
+  return static_cast<size_t>(kRmsMaxBlocks) * d * sizeof(float);
+}
+
+int run_rmsnorm_bwd(const dmf_rmsnorm_bwd_args* a) {
+  if (a == nullptr || a->weight == nullptr || a->dweight == nullptr) return DMF_ATTN_ERR_NULL;
+  int st = rms_check(a->batch, a->seqlen, a->heads, a->head_dim, a->dtype);
+  if (st != DMF_ATTN_OK) return st;
+  if ((st = check_tensor(a->dy, 2)) != DMF_ATTN_OK || (st = check_tensor(a->x, 2)) != DMF_ATTN_OK ||
+      (st = check_tensor(a->dx, 2)) != DMF_ATTN_OK)
+    return st;
+  if (a->workspace == nullptr || a->workspace_bytes < rmsnorm_bwd_workspace_bytes(a->head_dim))
+    return DMF_ATTN_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(a->workspace) & 15u) != 0) return DMF_ATTN_ERR_ALIGN;
+  int sm_count = 0;
+  if ((st = device_info(&sm_count)) != DMF_ATTN_OK) return st;
+  RmsParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.x = a->x.ptr; p.x_sb = a->x.stride_b; p.x_sl = a->x.stride_l; p.x_sh = a->x.stride_h;
+  p.dy = a->dy.ptr; p.dy_sb = a->dy.stride_b; p.dy_sl = a->dy.stride_l; p.dy_sh = a->dy.stride_h;
+  p.dx = a->dx.ptr; p.dx_sb = a->dx.stride_b; p.dx_sl = a->dx.stride_l; p.dx_sh = a->dx.stride_h;
+  p.w = a->weight;
+  p.dw_partial = static_cast<float*>(a->workspace);
+  p.batch = a->batch; p.seqlen = a->seqlen; p.heads = a->heads; p.head_dim = a->head_dim;
+  p.rows = static_cast<int64_t>(a->batch) * a->seqlen * a->heads;
+  p.eps = a->eps;
+  const int grid = rms_grid(p.rows, a->head_dim, kRmsUnrollBwd, sm_count);
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (a->dtype == DMF_ATTN_BF16) rms_launch_bwd<__nv_bfloat16>(a->head_dim / 8, grid, stream, p);
+  else rms_launch_bwd<__half>(a->head_dim / 8, grid, stream, p);
+  if (cudaGetLastError() != cudaSuccess) return DMF_ATTN_ERR_LAUNCH;
+  rmsnorm_dw_reduce_kernel<<<(a->head_dim + 31) / 32, 1024, 0, stream>>>(p.dw_partial, a->dweight, grid, a->head_dim);
+  return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
+}
+
 }  // namespace
 
 #define DMF_API __attribute__((visibility("default")))
@@ -550,6 +652,12 @@ DMF_API int dmf_attn_fwd(const dmf_attn_fwd_args* args) { return run_fwd(args, f
 DMF_API int dmf_attn_validate_fwd(const dmf_attn_fwd_args* args, int dual) { return validate_fwd(args, dual != 0); }
 
 DMF_API int dmf_attn_validate_bwd(const dmf_attn_bwd_args* args) { return validate_bwd(args); }
+
+DMF_API int dmf_rmsnorm_fwd(const dmf_rmsnorm_args* args) { return run_rmsnorm_fwd(args); }
+
+DMF_API size_t dmf_rmsnorm_bwd_workspace_bytes(int32_t head_dim) { return rmsnorm_bwd_workspace_bytes(head_dim); }
+
+DMF_API int dmf_rmsnorm_bwd(const dmf_rmsnorm_bwd_args* args) { return run_rmsnorm_bwd(args); }
 
 DMF_API size_t dmf_attn_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t seqlen_kv, int32_t heads,
                                     int32_t head_dim) {

@@ -20,6 +20,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..flash_attn_jvp import flash_attn_func
+from ..rms_norm import rms_norm
 
 
 def attn_op(q, k, v, op: str = "base"):
@@ -38,14 +39,20 @@ def attn_op(q, k, v, op: str = "base"):
 
 
 class RMSNorm(nn.Module):
-    """models/layers.py:33-42."""
+    """models/layers.py:33-42.  With ``fused`` the per-head norm of a 16-bit (B, L, H, D) CUDA tensor runs as
+    the single-pass kernel of dmf_b200.rms_norm (tangent included under forward-mode AD); anything else takes
+    the reference's elementwise form below."""
 
-    def __init__(self, dim: int, eps: float = 1e-6):
+    def __init__(self, dim: int, eps: float = 1e-6, fused: bool = False):
         super().__init__()
         self.eps = eps
+        self.fused = fused
         self.scale = nn.Parameter(torch.ones(dim))
 
     def forward(self, x):
+        if (self.fused and x.is_cuda and x.dim() == 4 and x.dtype in (torch.bfloat16, torch.float16)
+                and x.shape[-1] % 8 == 0 and x.shape[-1] <= 128):
+            return rms_norm(x, self.scale, self.eps)
         norm_x = torch.rsqrt(x.pow(2).mean(-1, keepdim=True, dtype=torch.float32) + self.eps)
         return x * norm_x.to(dtype=x.dtype) * self.scale.to(dtype=x.dtype)
 
@@ -103,8 +110,9 @@ class Attention(nn.Module):
         assert dim % num_heads == 0
         self.num_heads, self.head_dim = num_heads, dim // num_heads
         self.qkv = nn.Linear(dim, dim * 3, bias=qkv_bias)
-        self.q_norm = RMSNorm(self.head_dim) if qk_norm else nn.Identity()
-        self.k_norm = RMSNorm(self.head_dim) if qk_norm else nn.Identity()
+        fused = attn_func in ("fa2", "fa3")   # the B200 ops travel together
+        self.q_norm = RMSNorm(self.head_dim, fused=fused) if qk_norm else nn.Identity()
+        self.k_norm = RMSNorm(self.head_dim, fused=fused) if qk_norm else nn.Identity()
         self.proj = nn.Linear(dim, dim, bias=proj_bias)
         self.attn = partial(attn_op, op=attn_func)
 

@@ -196,3 +196,98 @@ def attn_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
 @torch.library.register_fake("dmf_b200::attn_bwd")
 def _attn_bwd_fake(dout, q, k, v, o, lse, softmax_scale):
     return (q.new_empty(q.shape), k.new_empty(k.shape), v.new_empty(v.shape))
+
+
+# ---- per-head RMS norm of q / k with its tangent (models/layers.py:33-42 under forward-mode AD) ----
+
+def _rms_weight(weight: torch.Tensor, device) -> torch.Tensor:
+    w = weight.detach()
+    if w.dtype != torch.float32 or w.device != device or not w.is_contiguous():
+        w = w.to(device=device, dtype=torch.float32).contiguous()
+    return w
+
+
+def rmsnorm_fwd_raw(x, tx, weight, eps: float):
+    """y (and ty if tx is given) for (B, L, H, D) tensors; one kernel, every row read and written once."""
+    tensors = (x,) if tx is None else (x, tx)
+    _check_inputs(*tensors)
+    if tx is not None and tx.shape != x.shape:
+        raise ValueError("shape mismatch between x and its tangent")
+    x = _prep(x)
+    tx = None if tx is None else _prep(tx)
+    B, L, H, D = x.shape
+    with torch.cuda.device(x.device):
+        w = _rms_weight(weight, x.device)
+        y = torch.empty((B, L, H, D), dtype=x.dtype, device=x.device)
+        ty = None if tx is None else torch.empty((B, L, H, D), dtype=x.dtype, device=x.device)
+        a = _lib.RmsNormArgs()
+        a.batch, a.seqlen, a.heads, a.head_dim = B, L, H, D
+        a.dtype = _DTYPES[x.dtype]
+        a.eps = float(eps)
+        a.x, a.y = _t4(x), _t4(y)
+        if tx is not None:
+            a.tx, a.ty = _t4(tx), _t4(ty)
+        a.weight = w.data_ptr()
+        a.stream = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(_lib.load().dmf_rmsnorm_fwd(C.byref(a)))
+        global launch_count
+        launch_count += 1
+    return y, ty
+
+
+def rmsnorm_bwd_raw(dy, x, weight, eps: float):
+    """dx (like x) and dweight (D, fp32) of y = rmsnorm(x) * weight."""
+    _check_inputs(dy, x)
+    dy, x = _prep(dy), _prep(x)
+    B, L, H, D = x.shape
+    with torch.cuda.device(x.device):
+        w = _rms_weight(weight, x.device)
+        dx = torch.empty((B, L, H, D), dtype=x.dtype, device=x.device)
+        dw = torch.empty((D,), dtype=torch.float32, device=x.device)
+        lib = _lib.load()
+        nbytes = lib.dmf_rmsnorm_bwd_workspace_bytes(D)
+        ws = torch.empty((nbytes,), dtype=torch.uint8, device=x.device)
+        a = _lib.RmsNormBwdArgs()
+        a.batch, a.seqlen, a.heads, a.head_dim = B, L, H, D
+        a.dtype = _DTYPES[x.dtype]
+        a.eps = float(eps)
+        a.dy, a.x, a.dx = _t4(dy), _t4(x), _t4(dx)
+        a.weight, a.dweight = w.data_ptr(), dw.data_ptr()
+        a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+        a.stream = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(lib.dmf_rmsnorm_bwd(C.byref(a)))
+        global launch_count
+        launch_count += 2
+    return dx, dw
+
+
+@torch.library.custom_op("dmf_b200::rmsnorm_fwd_dual", mutates_args=(), device_types="cuda")
+def rmsnorm_fwd_dual(x: torch.Tensor, tx: torch.Tensor, weight: torch.Tensor,
+                     eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    return rmsnorm_fwd_raw(x, tx, weight, eps)
+
+
+@torch.library.register_fake("dmf_b200::rmsnorm_fwd_dual")
+def _rmsnorm_fwd_dual_fake(x, tx, weight, eps):
+    return x.new_empty(x.shape), x.new_empty(x.shape)
+
+
+@torch.library.custom_op("dmf_b200::rmsnorm_fwd", mutates_args=(), device_types="cuda")
+def rmsnorm_fwd(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    return rmsnorm_fwd_raw(x, None, weight, eps)[0]
+
+
+@torch.library.register_fake("dmf_b200::rmsnorm_fwd")
+def _rmsnorm_fwd_fake(x, weight, eps):
+    return x.new_empty(x.shape)
+
+
+@torch.library.custom_op("dmf_b200::rmsnorm_bwd", mutates_args=(), device_types="cuda")
+def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+                eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    return rmsnorm_bwd_raw(dy, x, weight, eps)
+
+
+@torch.library.register_fake("dmf_b200::rmsnorm_bwd")
+def _rmsnorm_bwd_fake(dy, x, weight, eps):
+    return x.new_empty(x.shape), x.new_empty((x.shape[-1],), dtype=torch.float32)

@@ -191,6 +191,58 @@ int dmf_attn_check_status_word(const int32_t* status_word, void* stream, int32_t
 int dmf_attn_validate_fwd(const dmf_attn_fwd_args* args, int dual);
 int dmf_attn_validate_bwd(const dmf_attn_bwd_args* args);
 
+/*
+ * Per-head RMS normalisation of q or k, with its tangent, and its primal backward.
+ *
+ * Replaces RMSNorm.forward of the reference's attention block (models/layers.py:33-42, applied to
+ * q and k at layers.py:148) and what PyTorch's forward-mode AD makes of it under torch.func.jvp:
+ *   r = rsqrt(mean_d(x^2) + eps)    y = x r w    ty = (tx r - x r^3 mean_d(x tx)) w
+ * x, tx, y, ty: (B, L, H, D) tensors in the layout rules above (tx.ptr == NULL: no tangent, ty is
+ * not written); weight: D floats in device memory (the module's parameter; it is rounded to the
+ * tensors' 16-bit type before use, as the reference casts it).  head_dim: a multiple of 8, at most
+ * 128; seqlen: any positive value.  Arithmetic is fp32 with one rounding of the result.
+ */
+typedef struct dmf_rmsnorm_args {
+  int32_t batch;
+  int32_t seqlen;
+  int32_t heads;
+  int32_t head_dim;
+  int32_t dtype;          /* enum dmf_attn_dtype */
+  float eps;              /* the reference uses 1e-6 */
+  dmf_attn_tensor x, tx;  /* read only */
+  dmf_attn_tensor y, ty;  /* out */
+  const float* weight;    /* (D) */
+  void* stream;           /* cudaStream_t */
+} dmf_rmsnorm_args;
+
+int dmf_rmsnorm_fwd(const dmf_rmsnorm_args* args);
+
+/*
+ * Backward of y with respect to x and weight (the tangent output carries no gradient, like the
+ * attention's): dx = r g - x r^3 mean_d(x g) with g = dy w, dweight_d = sum over rows of dy_d x_d r.
+ * dweight: D floats, overwritten.  workspace: device memory of at least
+ * dmf_rmsnorm_bwd_workspace_bytes(head_dim) bytes (per-block partial sums of dweight, reduced in a
+ * fixed order: the result is bit-reproducible); its contents on entry do not matter.
+ */
+typedef struct dmf_rmsnorm_bwd_args {
+  int32_t batch;
+  int32_t seqlen;
+  int32_t heads;
+  int32_t head_dim;
+  int32_t dtype;
+  float eps;
+  dmf_attn_tensor dy, x;  /* read only */
+  dmf_attn_tensor dx;     /* out */
+  const float* weight;    /* (D) */
+  float* dweight;         /* out, (D) */
+  void* workspace;
+  size_t workspace_bytes;
+  void* stream;
+} dmf_rmsnorm_bwd_args;
+
+size_t dmf_rmsnorm_bwd_workspace_bytes(int32_t head_dim);
+int dmf_rmsnorm_bwd(const dmf_rmsnorm_bwd_args* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -178,6 +178,28 @@ def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, eps: float 
     return x * norm_x.to(dtype=x.dtype) * w
 
 
+def rms_norm_jvp_closed_form(x, tx, weight, eps: float = 1e-6):
+    """fp64 closed form of RMSNorm (models/layers.py:39-42) and of its tangent with respect to x:
+    r = rsqrt(mean(x^2) + eps), y = x r w, ty = (tx r - x r^3 mean(x tx)) w.  The weight is rounded
+    to x's dtype first, as the reference casts it.  Returns (y, ty) in fp64."""
+    w = weight.to(x.dtype).double()
+    xd, td = x.double(), tx.double()
+    r = torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps)
+    y = xd * r * w
+    ty = (td * r - xd * r.pow(3) * (xd * td).mean(-1, keepdim=True)) * w
+    return y, ty
+
+
+def rms_norm_bwd_closed_form(dy, x, weight, eps: float = 1e-6):
+    """fp64 gradients of y = RMSNorm(x) w with respect to x and w (autograd of the formula above)."""
+    w = weight.to(x.dtype).double()
+    xd, g = x.double(), dy.double() * w
+    r = torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps)
+    dx = r * g - xd * r.pow(3) * (xd * g).mean(-1, keepdim=True)
+    dw = (dy.double() * xd * r).reshape(-1, x.shape[-1]).sum(0)
+    return dx, dw
+
+
 # ----------------------------------------------------------------------------
 # seeded synthetic inputs with the shapes / distributions of the named configs
 # ----------------------------------------------------------------------------

@@ -15,7 +15,7 @@ ROOT = Path(__file__).resolve().parent.parent
 def _declared_symbols():
     text = (ROOT / "include" / "dmf_attn.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(dmf_attn_[a-z_0-9]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(dmf_(?:attn|rmsnorm)_[a-z_0-9]+)\s*\(", text)))
 
 
 def test_library_loads_and_exports_header_symbols():

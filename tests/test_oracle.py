@@ -90,3 +90,21 @@ def test_config_shapes_and_flops():
     assert abs(orc.flops_dual_fwd(256, 16, 256, 256, 72) - 231.9e9) < 0.1e9
     assert abs(orc.flops_dual_fwd(64, 16, 1024, 1024, 72) - 927.7e9) < 0.1e9
     assert abs(orc.flops_dual_fwd(8, 12, 256, 256, 64) - 4.83e9) < 0.01e9
+
+
+def test_rms_norm_closed_forms_match_autodiff_of_the_reference_form():
+    """rms_norm restates RMSNorm.forward (models/layers.py:39-42; pinned against the reference's own output by
+    the qk-norm golden case above); the fp64 closed forms of its tangent and gradients must agree with
+    torch.func.jvp / autograd through it."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 8, 3, 72, generator=g, dtype=torch.float64)
+    tx = torch.randn(2, 8, 3, 72, generator=g, dtype=torch.float64)
+    w = (1 + 0.2 * torch.randn(72, generator=g)).double()
+    dy = torch.randn(2, 8, 3, 72, generator=g, dtype=torch.float64)
+    y, ty = torch.func.jvp(lambda a: orc.rms_norm(a, w), (x,), (tx,))
+    y2, ty2 = orc.rms_norm_jvp_closed_form(x, tx, w)
+    assert float((y - y2).abs().max()) < 1e-5 and float((ty - ty2).abs().max()) < 1e-5   # the reference form means in fp32
+    xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    orc.rms_norm(xg, wg).backward(dy)
+    dx, dw = orc.rms_norm_bwd_closed_form(dy, x, w)
+    assert float((xg.grad - dx).abs().max()) < 1e-5 and float((wg.grad - dw).abs().max()) < 1e-5
