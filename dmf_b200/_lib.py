@@ -1,4 +1,4 @@
-"""ctypes binding of the C ABI in include/dmf_attn.h.
+"""ctypes binding of the C ABI in include/dmf_attn.h and include/dmf_adaln.h.
 
 The library is the only compute path of this package: if it cannot be loaded the
 import fails; nothing falls back to PyTorch or to the CPU.
@@ -21,13 +21,16 @@ STATUS_NAMES = {
     11: "ERR_WORKSPACE", 12: "ERR_TIMEOUT", 13: "ERR_TOO_LARGE",
 }
 
-# every symbol include/dmf_attn.h declares
+# every symbol include/dmf_attn.h and include/dmf_adaln.h declare
 EXPORTS = (
     "dmf_attn_abi_version", "dmf_attn_status_string", "dmf_attn_fwd_dual", "dmf_attn_fwd",
     "dmf_attn_bwd", "dmf_attn_bwd_static", "dmf_attn_bwd_workspace_bytes", "dmf_attn_check_status_word",
     "dmf_attn_validate_fwd", "dmf_attn_validate_bwd",
     "dmf_rmsnorm_fwd", "dmf_rmsnorm_bwd", "dmf_rmsnorm_bwd_workspace_bytes",
+    "dmf_ln_modulate_fwd", "dmf_ln_modulate_bwd", "dmf_adaln_bwd_workspace_bytes",
+    "dmf_gate_residual_fwd", "dmf_gate_residual_bwd",
 )
+ADALN_BF16, ADALN_F32 = 0, 2
 
 
 class Tensor4(C.Structure):
@@ -73,6 +76,51 @@ class RmsNormBwdArgs(C.Structure):
         ("dtype", C.c_int32), ("eps", C.c_float),
         ("dy", Tensor4), ("x", Tensor4), ("dx", Tensor4),
         ("weight", C.c_void_p), ("dweight", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
+class Rows(C.Structure):
+    """dmf_rows: a (B, L, C) tensor, element strides of B and L."""
+    _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_l", C.c_int64)]
+
+
+class Mod(C.Structure):
+    """dmf_mod: a (B, C) tensor, element stride of B."""
+    _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64)]
+
+
+_ADA_HEAD = [("batch", C.c_int32), ("seqlen", C.c_int32), ("channels", C.c_int32),
+             ("wide_dtype", C.c_int32), ("narrow_dtype", C.c_int32), ("mod_dtype", C.c_int32)]
+
+
+class LnModulateArgs(C.Structure):
+    _fields_ = _ADA_HEAD + [
+        ("eps", C.c_float), ("reserved", C.c_int32),
+        ("x", Rows), ("tx", Rows), ("shift", Mod), ("scale", Mod), ("tshift", Mod), ("tscale", Mod),
+        ("y", Rows), ("ty", Rows), ("stream", C.c_void_p),
+    ]
+
+
+class LnModulateBwdArgs(C.Structure):
+    _fields_ = _ADA_HEAD + [
+        ("eps", C.c_float), ("reserved", C.c_int32),
+        ("dy", Rows), ("x", Rows), ("scale", Mod), ("dx", Rows),
+        ("dshift", C.c_void_p), ("dscale", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
+class GateResidualArgs(C.Structure):
+    _fields_ = _ADA_HEAD + [
+        ("x", Rows), ("tx", Rows), ("h", Rows), ("th", Rows), ("gate", Mod), ("tgate", Mod),
+        ("out", Rows), ("tout", Rows), ("stream", C.c_void_p),
+    ]
+
+
+class GateResidualBwdArgs(C.Structure):
+    _fields_ = _ADA_HEAD + [
+        ("dout", Rows), ("h", Rows), ("gate", Mod), ("dh", Rows), ("dgate", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
     ]
 
@@ -126,6 +174,13 @@ def load() -> C.CDLL:
         lib.dmf_rmsnorm_bwd.argtypes = [C.POINTER(RmsNormBwdArgs)]
         lib.dmf_rmsnorm_bwd_workspace_bytes.restype = C.c_size_t
         lib.dmf_rmsnorm_bwd_workspace_bytes.argtypes = [C.c_int32]
+        for name, args in (("dmf_ln_modulate_fwd", LnModulateArgs), ("dmf_ln_modulate_bwd", LnModulateBwdArgs),
+                           ("dmf_gate_residual_fwd", GateResidualArgs), ("dmf_gate_residual_bwd", GateResidualBwdArgs)):
+            fn = getattr(lib, name)
+            fn.restype = C.c_int
+            fn.argtypes = [C.POINTER(args)]
+        lib.dmf_adaln_bwd_workspace_bytes.restype = C.c_size_t
+        lib.dmf_adaln_bwd_workspace_bytes.argtypes = [C.c_int32] * 3
         got = lib.dmf_attn_abi_version()
         if got != ABI_VERSION:
             raise ImportError(f"libdmf_attn.so has ABI version {got}, this package expects {ABI_VERSION}")

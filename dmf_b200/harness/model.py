@@ -20,6 +20,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..flash_attn_jvp import flash_attn_func
+from .. import adaln
 from ..rms_norm import rms_norm
 
 
@@ -150,9 +151,14 @@ class DiTBlock(nn.Module):
         self.norm2 = nn.LayerNorm(hidden_size, elementwise_affine=False, eps=1e-6)
         self.mlp = Mlp(hidden_size, int(hidden_size * mlp_ratio))
         self.adaLN_modulation = nn.Sequential(nn.SiLU(), nn.Linear(hidden_size, 6 * hidden_size))
+        self.fused = block_kwargs.get("attn_func", "base") in ("fa2", "fa3")   # the B200 ops travel together
 
     def forward(self, x, c):
         sh_a, sc_a, g_a, sh_m, sc_m, g_m = self.adaLN_modulation(c).chunk(6, dim=-1)
+        if self.fused and adaln.usable(x):
+            # one kernel each (primal + tangent under forward-mode AD) instead of the elementwise forms below
+            x = adaln.gate_residual(x, g_a, self.attn(adaln.ln_modulate(x, sh_a, sc_a, self.norm1.eps)))
+            return adaln.gate_residual(x, g_m, self.mlp(adaln.ln_modulate(x, sh_m, sc_m, self.norm2.eps)))
         x = x + g_a * self.attn(modulate(self.norm1(x), sh_a, sc_a))
         x = x + g_m * self.mlp(modulate(self.norm2(x), sh_m, sc_m))
         return x
@@ -164,9 +170,12 @@ class FinalLayer(nn.Module):
         self.norm_final = nn.LayerNorm(hidden_size, elementwise_affine=False, eps=1e-6)
         self.linear = nn.Linear(hidden_size, patch_size * patch_size * out_channels)
         self.adaLN_modulation = nn.Sequential(nn.SiLU(), nn.Linear(hidden_size, 2 * hidden_size))
+        self.fused = False   # set by DMFT when the blocks use the B200 ops
 
     def forward(self, x, c):
         shift, scale = self.adaLN_modulation(c).chunk(2, dim=-1)
+        if self.fused and adaln.usable(x):
+            return self.linear(adaln.ln_modulate(x, shift, scale, self.norm_final.eps))
         return self.linear(modulate(self.norm_final(x), shift, scale))
 
 
@@ -200,6 +209,7 @@ class DMFT(nn.Module):
         self.blocks = nn.ModuleList([DiTBlock(hidden_size, num_heads, mlp_ratio=mlp_ratio, **block_kwargs)
                                      for _ in range(depth)])
         self.final_layer = FinalLayer(hidden_size, patch_size, self.out_channels)
+        self.final_layer.fused = block_kwargs.get("attn_func", "base") in ("fa2", "fa3")
         if use_logvar:
             self.logvar_linear = nn.Linear(256, 1)
         self.initialize_weights()

@@ -13,9 +13,9 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def _declared_symbols():
-    text = (ROOT / "include" / "dmf_attn.h").read_text()
+    text = "".join(h.read_text() for h in sorted((ROOT / "include").glob("*.h")))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(dmf_(?:attn|rmsnorm)_[a-z_0-9]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(dmf_[a-z_0-9]+)\s*\(", text)))
 
 
 def test_library_loads_and_exports_header_symbols():
@@ -106,3 +106,36 @@ def test_compute_entry_points_fail_loudly_without_a_gpu():
     q = torch.randn(1, 128, 1, 64)
     with pytest.raises(Exception):
         flash_attn_func(q, q, q)
+
+
+def test_adaln_entry_points_reject_bad_arguments_without_a_gpu():
+    lib = _lib.load()
+    fake = 0x10000
+    a = _lib.LnModulateArgs()
+    a.batch, a.seqlen, a.channels = 2, 16, 1152
+    a.wide_dtype, a.narrow_dtype, a.mod_dtype = _lib.ADALN_F32, _lib.ADALN_BF16, _lib.ADALN_BF16
+    a.x, a.y = _lib.Rows(fake, 16 * 1152, 1152), _lib.Rows(fake, 16 * 1152, 1152)
+    a.shift, a.scale = _lib.Mod(fake, 6 * 1152), _lib.Mod(fake, 6 * 1152)
+    assert lib.dmf_ln_modulate_fwd(None) == 1
+    a.channels = 1000
+    assert lib.dmf_ln_modulate_fwd(C.byref(a)) == 5          # width not compiled
+    a.channels = 1152
+    a.wide_dtype, a.narrow_dtype = _lib.ADALN_BF16, _lib.ADALN_F32
+    assert lib.dmf_ln_modulate_fwd(C.byref(a)) == 2          # a bf16 stream with fp32 matmul side
+    a.wide_dtype, a.narrow_dtype = _lib.ADALN_F32, _lib.ADALN_BF16
+    a.x = _lib.Rows(fake + 4, 16 * 1152, 1152)
+    assert lib.dmf_ln_modulate_fwd(C.byref(a)) == 7          # base not 16-byte aligned
+    a.x = _lib.Rows(fake, 16 * 1152, 1150)
+    assert lib.dmf_ln_modulate_fwd(C.byref(a)) == 6          # row stride not a multiple of 4 elements
+    a.x = _lib.Rows(fake, 16 * 1152, 1152)
+    a.scale = _lib.Mod(None, 0)
+    assert lib.dmf_ln_modulate_fwd(C.byref(a)) == 1
+    a.scale = _lib.Mod(fake, 6 * 1152)
+    assert lib.dmf_ln_modulate_fwd(C.byref(a)) == 8          # all checks pass: no device here
+    assert lib.dmf_adaln_bwd_workspace_bytes(4, 100, 1152) == 4 * 4 * 2 * 1152 * 4
+    b = _lib.GateResidualBwdArgs()
+    b.batch, b.seqlen, b.channels = 2, 16, 768
+    b.wide_dtype, b.narrow_dtype, b.mod_dtype = _lib.ADALN_F32, _lib.ADALN_BF16, _lib.ADALN_BF16
+    b.dout, b.h, b.dh = (_lib.Rows(fake, 16 * 768, 768) for _ in range(3))
+    b.gate, b.dgate = _lib.Mod(fake, 768), fake
+    assert lib.dmf_gate_residual_bwd(C.byref(b)) == 11       # no workspace

@@ -70,8 +70,9 @@ def test_train_step_and_sampler_run():
     n0 = ops.launch_count
     loss = T.train_step(st, [T.synthetic_batch(st, 4), T.synthetic_batch(st, 4)])
     assert torch.isfinite(loss)
-    # per micro-batch: 12 plain forwards + 12 dual forwards + 24 backward calls of 2 kernels
-    assert ops.launch_count - n0 == 2 * (12 + 12 + 24 * 2)
+    # per micro-batch, two passes over 12 blocks (plain + dual), each backpropagated (a backward call = 2 kernels):
+    # attention 24 forwards, LayerNorm-modulate 2 per block + the final layer = 50, gate-residual 2 per block = 48
+    assert ops.launch_count - n0 == 2 * (24 + 50 + 48) * (1 + 2)
     assert any(not torch.equal(v, before[k]) for k, v in st.model.state_dict().items())
     model = st.model.to(torch.bfloat16).eval()
     z = torch.randn(4, 4, 32, 32, device=DEV, dtype=torch.bfloat16)

@@ -108,3 +108,29 @@ def test_rms_norm_closed_forms_match_autodiff_of_the_reference_form():
     orc.rms_norm(xg, wg).backward(dy)
     dx, dw = orc.rms_norm_bwd_closed_form(dy, x, w)
     assert float((xg.grad - dx).abs().max()) < 1e-5 and float((wg.grad - dw).abs().max()) < 1e-5
+
+
+def test_adaln_closed_forms_match_autodiff_of_the_reference_forms():
+    """oracle/adaln_oracle.py restates modulate(norm(x)) and x + gate * h (models/layers.py:28-29, 195-201); the fp64
+    closed forms the kernels implement must agree with torch.func.jvp / autograd through the restated forms."""
+    from oracle import adaln_oracle as ada
+    g = torch.Generator().manual_seed(11)
+    B, L, Cn = 2, 5, 384
+    rn = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)
+    x, tx, h, th, dy = rn(B, L, Cn) * 2 + 0.3, rn(B, L, Cn), rn(B, L, Cn), rn(B, L, Cn), rn(B, L, Cn)
+    sh, sc, gt, tsh, tsc, tgt = (0.3 * rn(B, 1, Cn) for _ in range(6))
+    y, ty = torch.func.jvp(ada.ln_modulate, (x, sh, sc), (tx, tsh, tsc))
+    y2, ty2 = ada.ln_modulate_jvp_closed_form(x, tx, sh, sc, tsh, tsc)
+    assert float((y - y2).abs().max()) < 1e-10 and float((ty - ty2).abs().max()) < 1e-10
+    xs = [t.clone().requires_grad_(True) for t in (x, sh, sc)]
+    ada.ln_modulate(*xs).backward(dy)
+    for got, want in zip([t.grad for t in xs], [ada.ln_modulate_bwd_closed_form(dy, x, sc)[i] for i in (0, 1, 2)]):
+        assert float((got - want).abs().max()) < 1e-10
+    o, to = torch.func.jvp(ada.gate_residual, (x, gt, h), (tx, tgt, th))
+    o2, to2 = ada.gate_residual_jvp_closed_form(x, tx, h, th, gt, tgt)
+    assert float((o - o2).abs().max()) < 1e-12 and float((to - to2).abs().max()) < 1e-12
+    xs = [t.clone().requires_grad_(True) for t in (x, gt, h)]
+    ada.gate_residual(*xs).backward(dy)
+    dx, dh, dg = ada.gate_residual_bwd_closed_form(dy, h, gt)
+    for got, want in zip([t.grad for t in xs], [dx, dg, dh]):
+        assert float((got - want).abs().max()) < 1e-10
