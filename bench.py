@@ -444,7 +444,7 @@ def run_model(args):
     from dmf_b200 import ops
     from dmf_b200.harness import train as T
     from dmf_b200.harness.model import build_dmft
-    from dmf_b200.harness.sampler import euler_sampler
+    from dmf_b200.harness.sampler import GraphedSampler, euler_sampler
 
     def sync_all():
         if world > 1:
@@ -462,7 +462,8 @@ def run_model(args):
         global_batch, mb = 256, args.micro_batch
         assert global_batch % (mb * world) == 0, "256 must be divisible by micro_batch * n_gpus"
         n_micro = global_batch // (mb * world)
-        st = T.build_train_state(dev, name=args.model, input_size=32, dmf_depth=20, attn_func="fa3", seed=0)
+        st = T.build_train_state(dev, name=args.model, input_size=32, dmf_depth=20, attn_func="fa3", seed=0,
+                                 graphs=not args.no_graphs)
         gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
         # the step's inputs start in pinned host memory: latents N(0,1), labels uniform
         host = [(torch.randn(mb, 4, 32, 32, generator=gen).pin_memory(),
@@ -475,7 +476,9 @@ def run_model(args):
 
         units, metric, unit, scaling = global_batch, "dmft_xl2_train_images_per_s", "images/s", "strong"
         desc = (f"{args.model} training step: FM forward + JVP forward + backward, bf16 autocast, global batch 256 = "
-                f"{world} GPU x {n_micro} micro-batches x {mb}, DDP gradient all-reduce, clip 1.0, fused AdamW, EMA")
+                f"{world} GPU x {n_micro} micro-batches x {mb}, "
+                + ("micro-batch forward+backward replayed as a CUDA graph, one NCCL all-reduce of the flat gradient buffer"
+                   if not args.no_graphs else "eager launches, DDP gradient all-reduce") + ", clip 1.0, fused AdamW, EMA")
         h2d = sum(x.numel() * x.element_size() + y.numel() * y.element_size() for x, y in host)
         d2h = 4
     else:
@@ -488,15 +491,22 @@ def run_model(args):
         y_host = torch.randint(0, 1000, (per_gpu,), generator=gen).pin_memory()
         out_host = torch.empty(per_gpu, 4, 64, 64, dtype=torch.float64).pin_memory()
 
+        graphed = None if args.no_graphs else GraphedSampler(model, per_gpu, (4, 64, 64), torch.bfloat16, dev,
+                                                              num_steps=4, shift=1.5, cfg_scale=1.0)
+
         def step():
-            z, y = z_host.to(dev, non_blocking=True), y_host.to(dev, non_blocking=True)
-            x = euler_sampler(model, z, y, num_steps=4, shift=1.5, cfg_scale=1.0)
+            if graphed is not None:      # the pinned host buffers are copied straight into the graph's inputs
+                x = graphed(z_host, y_host)
+            else:
+                z, y = z_host.to(dev, non_blocking=True), y_host.to(dev, non_blocking=True)
+                x = euler_sampler(model, z, y, num_steps=4, shift=1.5, cfg_scale=1.0)
             out_host.copy_(x, non_blocking=True)
             return x
 
         units, metric, unit, scaling = per_gpu * world, "dmft_xl2_sample_images_per_s", "images/s", "weak"
         desc = (f"{args.model} 4-step Euler sampling at 512px (latent 4x64x64, shift 1.5, qk-norm, bf16 weights), "
-                f"{per_gpu} images per GPU, no VAE decode")
+                f"{per_gpu} images per GPU, no VAE decode"
+                + ("" if args.no_graphs else ", the 4-step loop replayed as one CUDA graph"))
         h2d = z_host.numel() * 2 + y_host.numel() * 8
         d2h = out_host.numel() * 8
 
@@ -554,6 +564,7 @@ def main():
                          "global batch 256; C5: DMFT-XL/2 4-step Euler sampling at 512px, 64 images per GPU")
     ap.add_argument("--micro-batch", type=int, default=32, help="C4: images per forward/backward pass")
     ap.add_argument("--model", default="DMFT-XL/2", help="C4/C5: harness model name (smaller ones for smoke runs)")
+    ap.add_argument("--no-graphs", action="store_true", help="C4 / C5: eager launches (and DDP) instead of the CUDA-graphed micro-step / sampler loop")
     ap.add_argument("--op", choices=["dual", "fwd", "bwd", "rmsnorm"], default="dual",
                     help="C2/C3: entry point to time (default: the fused forward+tangent, which is the bench line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -61,7 +61,9 @@ class RMSNorm(nn.Module):
 def timestep_embedding(t, dim: int, max_period: int = 10000):
     """models/layers.py:46-55: [cos | sin] of t * geometric frequencies."""
     half = dim // 2
-    freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32) / half).to(t.device)
+    # built on t's device (the reference builds it on the host and copies, models/layers.py:50-51: a host-to-device
+    # copy per call, which also cannot be captured in a CUDA graph)
+    freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32, device=t.device) / half)
     args = t[..., None].float() * freqs[None]
     emb = torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
     if dim % 2:
