@@ -425,6 +425,88 @@ def run_rmsnorm(args):
             "op": "rmsnorm", "gpu_launches": 2 * args.steps, "clocks": sampler.summary()}))
 
 
+def run_adaln(args):
+    """The adaLN-Zero elementwise ops of one DiT block with tangents, at the workload's token count and the model
+    width H*D: a step is the block's two LayerNorm-modulates and two gate-residuals (fp32 stream, bf16 matmul side,
+    as in training under bf16 autocast)."""
+    import torch
+    from dmf_b200 import adaln
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, L, H, D, ts, _, desc = WORKLOADS[args.workload]
+    if args.batch is not None:
+        B = args.batch
+    Cn = H * D
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=gen)
+    x, tx = rn(B, L, Cn), rn(B, L, Cn) * ts
+    h, th = rn(B, L, Cn).to(torch.bfloat16), (rn(B, L, Cn) * ts).to(torch.bfloat16)
+    mods, tmods = (0.3 * rn(B, 1, 6 * Cn)).to(torch.bfloat16), (0.03 * rn(B, 1, 6 * Cn)).to(torch.bfloat16)
+    sh_a, sc_a, g_a, sh_m, sc_m, g_m = mods.chunk(6, dim=-1)
+    tsh_a, tsc_a, tg_a, tsh_m, tsc_m, tg_m = tmods.chunk(6, dim=-1)
+    per = {}
+
+    def ln(sh, sc, tsh, tsc):
+        return adaln.ln_modulate_fwd_raw(x, tx, sh, sc, tsh, tsc, 1e-6, torch.bfloat16)
+
+    def gate(g, tg):
+        return adaln.gate_residual_fwd_raw(x, tx, h, th, g, tg)
+
+    def step():
+        ln(sh_a, sc_a, tsh_a, tsc_a)
+        gate(g_a, tg_a)
+        ln(sh_m, sc_m, tsh_m, tsc_m)
+        return gate(g_m, tg_m)
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    n_el = B * L * Cn
+    ln_bytes = n_el * (4 + 4 + 2 + 2.0)        # x, tx fp32 in; y, ty bf16 out
+    gate_bytes = n_el * (4 + 4 + 2 + 2 + 4 + 4.0)  # x, tx fp32, h, th bf16 in; out, tout fp32 out
+    for _ in range(max(args.warmup, 3)):
+        step()
+    per["ln_modulate_dual_gbs"] = ln_bytes / (timed(lambda: ln(sh_a, sc_a, tsh_a, tsc_a), args.steps) * 1e-3) / 1e9
+    per["gate_residual_dual_gbs"] = gate_bytes / (timed(lambda: gate(g_a, tg_a), args.steps) * 1e-3) / 1e9
+    # the primal backwards (not part of the timed step): dy bf16, x fp32 in, dx fp32 out / dout fp32, h bf16 in, dh bf16 out
+    dy = rn(B, L, Cn).to(torch.bfloat16)
+    per["ln_modulate_bwd_gbs"] = n_el * 10.0 / (timed(lambda: adaln.ln_modulate_bwd_raw(dy, x, sc_a, 1e-6), args.steps) * 1e-3) / 1e9
+    per["gate_residual_bwd_gbs"] = n_el * 8.0 / (timed(lambda: adaln.gate_residual_bwd_raw(x, h, g_a), args.steps) * 1e-3) / 1e9
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    sampler.active.set()
+    ms = timed(step, args.steps)
+    sampler.active.clear()
+    sampler.stop()
+    nbytes = 2 * (ln_bytes + gate_bytes)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    peaks = _peaks()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "adaln_block_dual_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload} tokens (B={B}, L={L}), width {Cn}: the adaLN ops of one DiT block with "
+                                   "tangents (2 LayerNorm-modulate, 2 gate-residual), fp32 stream, bf16 matmul side",
+                       "l2": "every tensor is larger than the 126 MB L2; no flush between steps"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                         "peak_source": f"HBM copy, of {peaks['source']}", "algorithmic_bytes_per_step": nbytes,
+                         "kernel": "ln_modulate_fwd_kernel<f32, bf16, dual> x 2 + gate_residual_fwd_kernel<f32, bf16, dual> x 2",
+                         "per_kernel_gbs": per},
+            "op": "adaln", "gpu_launches": 4 * args.steps, "clocks": sampler.summary()}))
+
+
 def run_model(args):
     """Whole-model configurations: C4 (training step, data parallel with an NCCL gradient
     all-reduce) and C5 (4-step Euler sampling, sharded per rank, no collective)."""
@@ -565,7 +647,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=32, help="C4: images per forward/backward pass")
     ap.add_argument("--model", default="DMFT-XL/2", help="C4/C5: harness model name (smaller ones for smoke runs)")
     ap.add_argument("--no-graphs", action="store_true", help="C4 / C5: eager launches (and DDP) instead of the CUDA-graphed micro-step / sampler loop")
-    ap.add_argument("--op", choices=["dual", "fwd", "bwd", "rmsnorm"], default="dual",
+    ap.add_argument("--op", choices=["dual", "fwd", "bwd", "rmsnorm", "adaln"], default="dual",
                     help="C2/C3: entry point to time (default: the fused forward+tangent, which is the bench line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -584,6 +666,8 @@ def main():
         run_reference(args)
     elif args.op == "rmsnorm":
         run_rmsnorm(args)
+    elif args.op == "adaln":
+        run_adaln(args)
     else:
         run_ours(args)
 

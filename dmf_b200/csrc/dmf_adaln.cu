@@ -129,7 +129,9 @@ int run_ln_modulate_fwd(const dmf_ln_modulate_args* a) {
   p.batch = a->batch; p.seqlen = a->seqlen; p.channels = a->channels;
   p.mod_f32 = a->mod_dtype == DMF_ADALN_F32;
   p.eps = a->eps;
-  const int grid = row_grid(static_cast<int64_t>(a->batch) * a->seqlen, sms);
+  p.rows_per_block = kAdaFwdRowsPerBlock;
+  p.splits = (a->seqlen + kAdaFwdRowsPerBlock - 1) / kAdaFwdRowsPerBlock;
+  const dim3 grid(p.splits, a->batch);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   return with_types(a->wide_dtype, a->narrow_dtype, [&](auto tw, auto tn) {
     using TW = decltype(tw);
