@@ -4,6 +4,6 @@
     from dmf_b200.dropin import install             # makes the reference's imports resolve here
 """
 
-from .flash_attn_jvp import FlashAttnFunc, flash_attn_func  # noqa: F401
+from .flash_attn_jvp import FlashAttnFunc, flash_attn_func, flash_attn_qkvpacked_func  # noqa: F401
 
-__all__ = ["flash_attn_func", "FlashAttnFunc"]
+__all__ = ["flash_attn_func", "flash_attn_qkvpacked_func", "FlashAttnFunc"]

@@ -14,6 +14,10 @@ Same surface as models/flash_attention_2_jvp.py and models/flash_attention_3_jvp
   tangent inputs and the scale - the stop-gradient-on-tangent behaviour that
   loss.py:171-173 relies on.  ``jvp`` hands back the saved tangent output.
 
+* ``flash_attn_qkvpacked_func(qkv, softmax_scale=None)`` on the (B, L, 3, H, D) view of the packed projection
+  (models/layers.py:143-146 builds q, k, v as its slices): the same computation, but the backward writes dq, dk, dv
+  straight into one packed gradient instead of three tensors that autograd then copies together.
+
 Every compute step is a kernel of the sm_100a library; there is no Triton, no
 PyTorch fallback and no CPU path.
 """
@@ -86,3 +90,49 @@ def flash_attn_func(q, k, v, softmax_scale=None):
         return fwAD.make_dual(out, t_out)
     out, _, _ = FlashAttnFunc.apply(q, k, v, None, None, None, softmax_scale)
     return out
+
+
+class FlashAttnQKVPackedFunc(torch.autograd.Function):
+    """FlashAttnFunc on the (B, L, 3, H, D) packed projection; the gradient comes back packed."""
+
+    @staticmethod
+    def forward(qkv, tqkv, softmax_scale):
+        if softmax_scale is None:
+            softmax_scale = qkv.shape[-1] ** (-0.5)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        if tqkv is not None:
+            o, to, m = torch.ops.dmf_b200.attn_fwd_dual(q, k, v, tqkv[:, :, 0], tqkv[:, :, 1], tqkv[:, :, 2],
+                                                        float(softmax_scale))
+        else:
+            to = None
+            o, m = torch.ops.dmf_b200.attn_fwd(q, k, v, float(softmax_scale))
+        return o, m, to
+
+    @staticmethod
+    def setup_context(ctx, inputs, outputs):
+        qkv, tqkv, softmax_scale = inputs
+        o, m, to = outputs
+        ctx.save_for_backward(qkv, o, m)
+        if tqkv is not None:
+            ctx.save_for_forward(to)
+        ctx.softmax_scale = qkv.shape[-1] ** (-0.5) if softmax_scale is None else softmax_scale
+
+    @staticmethod
+    def backward(ctx, dout, *args):
+        qkv, o, m = ctx.saved_tensors
+        return torch.ops.dmf_b200.attn_bwd_qkvpacked(dout, qkv, o, m, float(ctx.softmax_scale)), None, None
+
+    @staticmethod
+    def jvp(ctx, *args):
+        t_saved = getattr(ctx, "saved_forward", ())
+        return (t_saved[0] if len(t_saved) > 0 else None), None, None
+
+
+def flash_attn_qkvpacked_func(qkv, softmax_scale=None):
+    if qkv.dim() != 5 or qkv.shape[2] != 3:
+        raise ValueError("expected a (B, L, 3, H, D) tensor")
+    primal, tangent = fwAD.unpack_dual(qkv)
+    if tangent is not None:
+        out, _, t_out = FlashAttnQKVPackedFunc.apply(primal, tangent, softmax_scale)
+        return fwAD.make_dual(out, t_out)
+    return FlashAttnQKVPackedFunc.apply(qkv, None, softmax_scale)[0]

@@ -19,7 +19,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..flash_attn_jvp import flash_attn_func
+from ..flash_attn_jvp import flash_attn_func, flash_attn_qkvpacked_func
 from .. import adaln
 from ..rms_norm import rms_norm
 
@@ -118,9 +118,14 @@ class Attention(nn.Module):
         self.k_norm = RMSNorm(self.head_dim, fused=fused) if qk_norm else nn.Identity()
         self.proj = nn.Linear(dim, dim, bias=proj_bias)
         self.attn = partial(attn_op, op=attn_func)
+        self.packed = fused and not qk_norm
 
     def forward(self, x):
         B, L, C = x.shape
+        if self.packed and x.is_cuda:
+            # same computation on the packed projection: its gradient is written packed, not copied together
+            qkv = self.qkv(x).reshape(B, L, 3, self.num_heads, self.head_dim)
+            return self.proj(flash_attn_qkvpacked_func(qkv).reshape(B, L, C))
         q, k, v = self.qkv(x).reshape(B, L, 3, self.num_heads, self.head_dim).permute(2, 0, 1, 3, 4).unbind(0)
         q, k = self.q_norm(q), self.k_norm(k)
         return self.proj(self.attn(q, k, v).reshape(B, L, C))

@@ -134,7 +134,9 @@ def fwd_raw(q, k, v, scale: float):
     return o, lse
 
 
-def bwd_raw(dout, q, k, v, o, lse, scale: float):
+def bwd_raw(dout, q, k, v, o, lse, scale: float, packed_out: bool = False):
+    """dq, dk, dv; with ``packed_out`` the three are the [:, :, i] views of one (B, L, 3, H, D) buffer, which is
+    returned instead (self-attention: q, k, v of equal shape)."""
     _check_inputs(dout, q, k, v, o)
     dout, q, k, v, o = (_prep(x) for x in (dout, q, k, v, o))
     lse = lse.contiguous()
@@ -142,9 +144,15 @@ def bwd_raw(dout, q, k, v, o, lse, scale: float):
     Lk = k.shape[1]
     lib = _lib.load()
     with torch.cuda.device(q.device):
-        dq, dk, dv = torch.empty_like(q, memory_format=torch.contiguous_format), \
-            torch.empty_like(k, memory_format=torch.contiguous_format), \
-            torch.empty_like(v, memory_format=torch.contiguous_format)
+        if packed_out:
+            if not (q.shape == k.shape == v.shape):
+                raise ValueError("a packed gradient needs q, k, v of one shape")
+            dqkv = torch.empty((B, Lq, 3, H, D), dtype=q.dtype, device=q.device)
+            dq, dk, dv = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+        else:
+            dq, dk, dv = torch.empty_like(q, memory_format=torch.contiguous_format), \
+                torch.empty_like(k, memory_format=torch.contiguous_format), \
+                torch.empty_like(v, memory_format=torch.contiguous_format)
         ws_bytes = lib.dmf_attn_bwd_workspace_bytes(B, Lq, Lk, H, D)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
         a = _lib.BwdArgs()
@@ -157,7 +165,7 @@ def bwd_raw(dout, q, k, v, o, lse, scale: float):
         launch_count += 2
         if _CHECK_EVERY_CALL:
             check_device_status(q.device)
-    return dq, dk, dv
+    return dqkv if packed_out else (dq, dk, dv)
 
 
 # ---- torch custom ops --------------------------------------------------------
@@ -196,6 +204,17 @@ def attn_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
 @torch.library.register_fake("dmf_b200::attn_bwd")
 def _attn_bwd_fake(dout, q, k, v, o, lse, softmax_scale):
     return (q.new_empty(q.shape), k.new_empty(k.shape), v.new_empty(v.shape))
+
+
+@torch.library.custom_op("dmf_b200::attn_bwd_qkvpacked", mutates_args=(), device_types="cuda")
+def attn_bwd_qkvpacked(dout: torch.Tensor, qkv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
+                       softmax_scale: float) -> torch.Tensor:
+    return bwd_raw(dout, qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], o, lse, softmax_scale, packed_out=True)
+
+
+@torch.library.register_fake("dmf_b200::attn_bwd_qkvpacked")
+def _attn_bwd_qkvpacked_fake(dout, qkv, o, lse, softmax_scale):
+    return qkv.new_empty(qkv.shape)
 
 
 # ---- per-head RMS norm of q / k with its tangent (models/layers.py:33-42 under forward-mode AD) ----

@@ -9,7 +9,7 @@ import pytest
 import torch
 import torch.autograd.forward_ad as fwAD
 
-from dmf_b200 import FlashAttnFunc, flash_attn_func
+from dmf_b200 import FlashAttnFunc, flash_attn_func, flash_attn_qkvpacked_func
 from oracle import attn_jvp_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -115,3 +115,26 @@ def test_torch_compile_traces_the_plain_path():
     f = torch.compile(lambda a, b, c: flash_attn_func(a, b, c) * 2, fullgraph=False, dynamic=True)
     out = f(q, k, v)
     assert orc.rel_l2(out.float(), 2 * flash_attn_func(q, k, v).float()) < 1e-6
+
+
+@pytest.mark.parametrize("D", [64, 72])
+def test_qkvpacked_is_the_same_computation_with_a_packed_gradient(D):
+    """flash_attn_qkvpacked_func on the (B, L, 3, H, D) projection against flash_attn_func on its slices: outputs,
+    tangents and gradients bit for bit (the same kernels on the same views; only where dq, dk, dv land differs)."""
+    q, k, v, dq, dk, dv, do = _ins(2, 256, 4, D, seed=D)
+    qkv = torch.stack([q, k, v], dim=2)
+    tqkv = torch.stack([dq, dk, dv], dim=2)
+    a = qkv.clone().requires_grad_(True)
+    u1, du1 = torch.func.jvp(flash_attn_qkvpacked_func, (a,), (tqkv,))
+    u1.backward(do)
+    b = qkv.clone().requires_grad_(True)
+    u2, du2 = torch.func.jvp(lambda t: flash_attn_func(t[:, :, 0], t[:, :, 1], t[:, :, 2]), (b,), (tqkv,))
+    u2.backward(do)
+    assert torch.equal(u1, u2) and torch.equal(du1, du2) and torch.equal(a.grad, b.grad)
+    assert a.grad.shape == qkv.shape and a.grad.is_contiguous()
+    c = qkv.clone().requires_grad_(True)
+    u3 = flash_attn_qkvpacked_func(c)                    # no tangent: the plain forward
+    u3.backward(do)
+    assert torch.equal(u3, u1) and torch.equal(c.grad, a.grad)
+    with pytest.raises(ValueError):
+        flash_attn_qkvpacked_func(q)
