@@ -9,9 +9,9 @@
 // LayerNorm kernels and the backward kernels are compiled per NV = C / 128 vectors per lane.
 // Arithmetic is fp32; the variance is the two-pass one (mean first, then centred squares).
 //
-// Backward kernels: the sums over l (dshift, dscale, dgate) are kept per lane in registers over the
-// rows of one (batch, row-range) block, added across the block's 8 warps through shared memory, and
-// written as one partial row per block; a second small kernel adds the partials of a batch in a
+// Backward kernels: the sums over l (dshift, dscale, dgate) are kept per warp (in shared memory for the
+// LayerNorm backward, in registers for the gate backward) over the rows of one (batch, row-range) block,
+// added across the block's 8 warps, and written as one partial row per block; a second small kernel adds the partials of a batch in a
 // fixed order (no atomics: bit-reproducible).
 #pragma once
 
@@ -48,8 +48,6 @@ struct AdaParams {
 
 constexpr int kAdaThreads = 256;
 constexpr int kAdaWarps = kAdaThreads / 32;
-constexpr int kAdaBwdRowsPerBlock = 32;
-constexpr int kAdaFwdRowsPerBlock = 32;
 
 __device__ __forceinline__ float ada_warp_sum(float v) {
 #pragma unroll
@@ -203,12 +201,16 @@ __device__ __forceinline__ void ada_block_column_sum(float (*red)[NV * 128], con
 
 // ---- backward of y = LayerNorm(x) (1 + scale) + shift ----
 // grid (splits, batch); block (s, b) owns rows [s * rows_per_block, (s + 1) * rows_per_block) of batch b.
+// The column sums of dshift / dscale are kept per warp in shared memory, not in registers: 72 registers less per
+// thread, two blocks per SM instead of one (4330 -> 5560 GB/s at 64 x 1024 rows of 1152 channels).
+// Dynamic shared memory: (1 + 16) * C floats.
 template <typename TW, typename TN, int NV>
-__global__ void __launch_bounds__(kAdaThreads) ln_modulate_bwd_kernel(const AdaParams p) {
+__global__ void __launch_bounds__(kAdaThreads, 2) ln_modulate_bwd_kernel(const AdaParams p) {
   constexpr int C = NV * 128;
   constexpr float kInvC = 1.f / static_cast<float>(C);
-  __shared__ float red[kAdaWarps][C];
-  __shared__ __align__(16) float s_sc[C];  // 1 + scale of this batch
+  extern __shared__ __align__(16) float ada_dyn[];
+  float* s_sc = ada_dyn;            // 1 + scale of this batch
+  float* s_acc = ada_dyn + C;       // [warp][shift | scale][C]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t b = blockIdx.y;
   const int l0 = blockIdx.x * p.rows_per_block;
@@ -219,12 +221,14 @@ __global__ void __launch_bounds__(kAdaThreads) ln_modulate_bwd_kernel(const AdaP
 #pragma unroll
     for (int i = 0; i < 4; ++i) s_sc[c + i] = 1.f + v[i];
   }
+  float* my_shift = s_acc + (warp * 2) * C;
+  float* my_scale = my_shift + C;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    *reinterpret_cast<float4*>(my_shift + 4 * (lane + 32 * k)) = make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(my_scale + 4 * (lane + 32 * k)) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   __syncthreads();
-  float a_shift[NV][4], a_scale[NV][4];
-#pragma unroll
-  for (int k = 0; k < NV; ++k)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) a_shift[k][i] = a_scale[k][i] = 0.f;
   for (int l = l0 + warp; l < l1; l += kAdaWarps) {
     const TW* xp = reinterpret_cast<const TW*>(p.x) + b * p.x_sb + l * p.x_sl;
     const TN* gp = reinterpret_cast<const TN*>(p.dy) + b * p.dy_sb + l * p.dy_sl;
@@ -251,17 +255,23 @@ __global__ void __launch_bounds__(kAdaThreads) ln_modulate_bwd_kernel(const AdaP
     float sg = 0.f, sgn = 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-      const float4 sv = *reinterpret_cast<const float4*>(s_sc + 4 * (lane + 32 * k));
+      const int c = 4 * (lane + 32 * k);
+      const float4 sv = *reinterpret_cast<const float4*>(s_sc + c);
       const float sc[4] = {sv.x, sv.y, sv.z, sv.w};
+      float4 a0 = *reinterpret_cast<float4*>(my_shift + c), a1 = *reinterpret_cast<float4*>(my_scale + c);
+      float* a0_ = reinterpret_cast<float*>(&a0);
+      float* a1_ = reinterpret_cast<float*>(&a1);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         x[k][i] *= r;  // n
-        a_shift[k][i] += g[k][i];
-        a_scale[k][i] = fmaf(g[k][i], x[k][i], a_scale[k][i]);
+        a0_[i] += g[k][i];
+        a1_[i] = fmaf(g[k][i], x[k][i], a1_[i]);
         g[k][i] *= sc[i];  // the gradient of n
         sg += g[k][i];
         sgn = fmaf(g[k][i], x[k][i], sgn);
       }
+      *reinterpret_cast<float4*>(my_shift + c) = a0;
+      *reinterpret_cast<float4*>(my_scale + c) = a1;
     }
     const float mg = ada_warp_sum(sg) * kInvC, mgn = ada_warp_sum(sgn) * kInvC;
     TW* dxp = reinterpret_cast<TW*>(p.dx) + b * p.dx_sb + l * p.dx_sl;
@@ -273,9 +283,15 @@ __global__ void __launch_bounds__(kAdaThreads) ln_modulate_bwd_kernel(const AdaP
       ada_store4(dxp + 4 * (lane + 32 * k), dx);
     }
   }
+  __syncthreads();
   float* prow = p.partial + ((b * p.splits + blockIdx.x) * 2) * C;
-  ada_block_column_sum<NV>(red, a_shift, prow);
-  ada_block_column_sum<NV>(red, a_scale, prow + C);
+  for (int c = threadIdx.x; c < 2 * C; c += kAdaThreads) {  // c < C: dshift, else dscale
+    const int q = c >= C, cc = c - q * C;
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAdaWarps; ++w) t += s_acc[(w * 2 + q) * C + cc];
+    prow[c] = t;
+  }
 }
 
 // out[q][b][c] = sum over s of partial[b][s][q][c], s in order.  grid (ceil(C / 256), batch, nq).

@@ -68,11 +68,23 @@ int row_grid(int64_t rows, int sm_count) {
   return static_cast<int>(want < cap ? want : cap);
 }
 
-int bwd_splits(int seqlen) { return (seqlen + kAdaBwdRowsPerBlock - 1) / kAdaBwdRowsPerBlock; }
+// Rows of one block: 32 where that still gives every SM a few blocks, fewer for small problems (a training
+// micro-batch of 32 x 256 tokens has 8192 rows).  A function of the shape only, so that the workspace size is too.
+int rows_per_block(int batch, int seqlen) {
+  constexpr int64_t kWantBlocks = 4 * 148;
+  for (int rpb = 32; rpb > 8; rpb /= 2)
+    if (static_cast<int64_t>(batch) * ((seqlen + rpb - 1) / rpb) >= kWantBlocks) return rpb;
+  return 8;
+}
+
+int bwd_splits(int batch, int seqlen) {
+  const int rpb = rows_per_block(batch, seqlen);
+  return (seqlen + rpb - 1) / rpb;
+}
 
 size_t bwd_workspace_bytes(int batch, int seqlen, int channels) {
   if (batch < 1 || seqlen < 1 || channels < 1) return 0;
-  return static_cast<size_t>(batch) * bwd_splits(seqlen) * 2 * channels * sizeof(float);
+  return static_cast<size_t>(batch) * bwd_splits(batch, seqlen) * 2 * channels * sizeof(float);
 }
 
 // (wide, narrow) -> types; NV -> the compiled widths
@@ -129,8 +141,8 @@ int run_ln_modulate_fwd(const dmf_ln_modulate_args* a) {
   p.batch = a->batch; p.seqlen = a->seqlen; p.channels = a->channels;
   p.mod_f32 = a->mod_dtype == DMF_ADALN_F32;
   p.eps = a->eps;
-  p.rows_per_block = kAdaFwdRowsPerBlock;
-  p.splits = (a->seqlen + kAdaFwdRowsPerBlock - 1) / kAdaFwdRowsPerBlock;
+  p.rows_per_block = rows_per_block(a->batch, a->seqlen);
+  p.splits = bwd_splits(a->batch, a->seqlen);
   const dim3 grid(p.splits, a->batch);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   return with_types(a->wide_dtype, a->narrow_dtype, [&](auto tw, auto tn) {
@@ -167,8 +179,8 @@ int run_ln_modulate_bwd(const dmf_ln_modulate_bwd_args* a) {
   p.partial = static_cast<float*>(a->workspace);
   p.batch = a->batch; p.seqlen = a->seqlen; p.channels = a->channels;
   p.mod_f32 = a->mod_dtype == DMF_ADALN_F32;
-  p.rows_per_block = kAdaBwdRowsPerBlock;
-  p.splits = bwd_splits(a->seqlen);
+  p.rows_per_block = rows_per_block(a->batch, a->seqlen);
+  p.splits = bwd_splits(a->batch, a->seqlen);
   p.eps = a->eps;
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   const dim3 grid(p.splits, a->batch);
@@ -176,7 +188,16 @@ int run_ln_modulate_bwd(const dmf_ln_modulate_bwd_args* a) {
     using TW = decltype(tw);
     using TN = decltype(tn);
     return with_width(a->channels, [&](auto nv) {
-      ln_modulate_bwd_kernel<TW, TN, decltype(nv)::value><<<grid, kAdaThreads, 0, stream>>>(p);
+      constexpr int NV = decltype(nv)::value;
+      constexpr int kSmem = (1 + 2 * kAdaWarps) * NV * 128 * static_cast<int>(sizeof(float));
+      static bool configured = false;  // per instantiation
+      if (!configured) {
+        if (cudaFuncSetAttribute(ln_modulate_bwd_kernel<TW, TN, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmem) != cudaSuccess)
+          return static_cast<int>(DMF_ATTN_ERR_LAUNCH);
+        configured = true;
+      }
+      ln_modulate_bwd_kernel<TW, TN, NV><<<grid, kAdaThreads, kSmem, stream>>>(p);
       return launched();
     });
   });
@@ -249,8 +270,8 @@ int run_gate_residual_bwd(const dmf_gate_residual_bwd_args* a) {
   p.partial = static_cast<float*>(a->workspace);
   p.batch = a->batch; p.seqlen = a->seqlen; p.channels = a->channels;
   p.mod_f32 = a->mod_dtype == DMF_ADALN_F32;
-  p.rows_per_block = kAdaBwdRowsPerBlock;
-  p.splits = bwd_splits(a->seqlen);
+  p.rows_per_block = rows_per_block(a->batch, a->seqlen);
+  p.splits = bwd_splits(a->batch, a->seqlen);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   const dim3 grid(p.splits, a->batch);
   st = with_types(a->wide_dtype, a->narrow_dtype, [&](auto tw, auto tn) {

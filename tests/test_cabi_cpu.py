@@ -132,7 +132,8 @@ def test_adaln_entry_points_reject_bad_arguments_without_a_gpu():
     assert lib.dmf_ln_modulate_fwd(C.byref(a)) == 1
     a.scale = _lib.Mod(fake, 6 * 1152)
     assert lib.dmf_ln_modulate_fwd(C.byref(a)) == 8          # all checks pass: no device here
-    assert lib.dmf_adaln_bwd_workspace_bytes(4, 100, 1152) == 4 * 4 * 2 * 1152 * 4
+    assert lib.dmf_adaln_bwd_workspace_bytes(4, 100, 1152) == 4 * 13 * 2 * 1152 * 4      # small problem: 8 rows per block
+    assert lib.dmf_adaln_bwd_workspace_bytes(64, 1024, 1152) == 64 * 32 * 2 * 1152 * 4  # 32 rows per block
     b = _lib.GateResidualBwdArgs()
     b.batch, b.seqlen, b.channels = 2, 16, 768
     b.wide_dtype, b.narrow_dtype, b.mod_dtype = _lib.ADALN_F32, _lib.ADALN_BF16, _lib.ADALN_BF16
