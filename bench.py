@@ -372,6 +372,46 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def _cpu_port_gbs(fn, nbytes, what, seconds=6.0):
+    """cpu_baseline of a memory-bound op: ``fn`` (the reference formulas under torch.func.jvp, fp32, all host threads)
+    timed for about ``seconds``; GB/s of the same algorithmic bytes the GPU figure counts."""
+    import torch
+    torch.set_num_threads(os.cpu_count() or 1)
+    first = _time_cpu(fn, 1, 1)[0]
+    n = int(min(2000, max(3, round(seconds / max(first, 1e-3)))))
+    times = _time_cpu(fn, n, 0)
+    return {"value": nbytes * len(times) / sum(times) / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(),
+            "kind": "port", "sample": f"{n} runs of {what}, {sum(times):.1f} s of CPU work"}
+
+
+def _e2e_gbs(host_in, run, n_out_bytes, nbytes, steps, dev):
+    """The same op from pinned host buffers: host-to-device copies of the inputs, the op, device-to-host copies of
+    the results, all inside the timed region."""
+    import torch
+    outs_host = None
+
+    def step():
+        nonlocal outs_host
+        outs = run([t.to(dev, non_blocking=True) for t in host_in])
+        if outs_host is None:
+            outs_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for h, o in zip(outs_host, outs):
+            h.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms,
+            "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in), "d2h_bytes_per_step": n_out_bytes}
+
+
 def run_rmsnorm(args):
     """The fused per-head RMS norm of q and k with tangents (one of the callers either side of the attention op):
     a step normalises q and k of a packed qkv projection of the workload's shape, with their tangents."""
@@ -410,6 +450,29 @@ def run_rmsnorm(args):
     nbytes = 2 * 4 * B * L * H * D * 2.0  # q and k: read x, tx; write y, ty
     gbs = nbytes / (ms * 1e-3) / 1e9
     peaks = _peaks()
+    cpu_base = e2e = None
+    if not args.no_e2e:
+        host = [t.contiguous().cpu().pin_memory() for t in (qkv[:, :, 0], qkv[:, :, 1], tqkv[:, :, 0], tqkv[:, :, 1])]
+
+        def run(d):
+            y0, t0 = ops.rmsnorm_fwd_raw(d[0], d[2], w, 1e-6)
+            y1, t1 = ops.rmsnorm_fwd_raw(d[1], d[3], w, 1e-6)
+            return [y0, t0, y1, t1]
+
+        e2e = _e2e_gbs(host, run, int(nbytes // 2), nbytes, min(args.steps, 10), dev)
+    if not args.no_cpu_baseline:
+        from oracle import attn_jvp_oracle as orc  # cpu_baseline leg only
+        cq, ctq = torch.randn(2, L, H, D), ts * torch.randn(2, L, H, D)
+        ck, ctk = torch.randn(2, L, H, D), ts * torch.randn(2, L, H, D)
+        cw = torch.ones(D)
+
+        def cstep():
+            with torch.no_grad():
+                torch.func.jvp(lambda a: orc.rms_norm(a, cw), (cq,), (ctq,))
+                return torch.func.jvp(lambda a: orc.rms_norm(a, cw), (ck,), (ctk,))
+
+        cpu_base = _cpu_port_gbs(cstep, nbytes * 2 / B, f"a B=2 batch slice of {args.workload}: the reference's RMSNorm "
+                                 "form (models/layers.py:39-42) under torch.func.jvp, fp32")
     if rank == 0:
         print(json.dumps({
             "metric": "qk_rmsnorm_dual_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
@@ -422,6 +485,7 @@ def run_rmsnorm(args):
                          "frac": gbs / peaks["hbm_gbs"], "traffic": None,
                          "peak_source": f"HBM copy, of {peaks['source']}", "algorithmic_bytes_per_step": nbytes,
                          "kernel": "rmsnorm_fwd_kernel<bf16, dual> x 2"},
+            "cpu_baseline": cpu_base, "e2e": e2e,
             "op": "rmsnorm", "gpu_launches": 2 * args.steps, "clocks": sampler.summary()}))
 
 
@@ -491,6 +555,34 @@ def run_adaln(args):
     nbytes = 2 * (ln_bytes + gate_bytes)
     gbs = nbytes / (ms * 1e-3) / 1e9
     peaks = _peaks()
+    cpu_base = e2e = None
+    if not args.no_e2e:
+        host = [t.cpu().pin_memory() for t in (x, tx, h, th)]
+
+        def run(d):
+            y, ty = adaln.ln_modulate_fwd_raw(d[0], d[1], sh_a, sc_a, tsh_a, tsc_a, 1e-6, torch.bfloat16)
+            o, to = adaln.gate_residual_fwd_raw(d[0], d[1], d[2], d[3], g_a, tg_a)
+            return [y, ty, o, to]
+
+        half = ln_bytes + gate_bytes   # one LayerNorm-modulate and one gate-residual from host buffers
+        e2e = _e2e_gbs(host, run, int(n_el * 12), half, min(args.steps, 10), dev)
+        e2e["note"] = "one LayerNorm-modulate + one gate-residual per step (half a block), modulation rows resident"
+    if not args.no_cpu_baseline:
+        from oracle import adaln_oracle as ada  # cpu_baseline leg only
+        cx, ctx_, ch, cth = (torch.randn(2, L, Cn) for _ in range(4))
+        cm, ctm = 0.3 * torch.randn(2, 1, 6 * Cn), 0.03 * torch.randn(2, 1, 6 * Cn)
+        c_sh, c_sc, c_g = cm.chunk(6, dim=-1)[:3]
+        c_tsh, c_tsc, c_tg = ctm.chunk(6, dim=-1)[:3]
+
+        def cstep():
+            with torch.no_grad():
+                for _ in range(2):
+                    torch.func.jvp(ada.ln_modulate, (cx, c_sh, c_sc), (ctx_, c_tsh, c_tsc))
+                    torch.func.jvp(ada.gate_residual, (cx, c_g, ch), (ctx_, c_tg, cth))
+
+        cpu_base = _cpu_port_gbs(cstep, nbytes * 2 / B, f"a B=2 batch slice of {args.workload} tokens: the reference's "
+                                 "modulate(norm(x)) and x + gate * h (models/layers.py:28-29, 195-201) under "
+                                 "torch.func.jvp, fp32")
     if rank == 0:
         print(json.dumps({
             "metric": "adaln_block_dual_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
@@ -504,6 +596,7 @@ def run_adaln(args):
                          "peak_source": f"HBM copy, of {peaks['source']}", "algorithmic_bytes_per_step": nbytes,
                          "kernel": "ln_modulate_fwd_kernel<f32, bf16, dual> x 2 + gate_residual_fwd_kernel<f32, bf16, dual> x 2",
                          "per_kernel_gbs": per},
+            "cpu_baseline": cpu_base, "e2e": e2e,
             "op": "adaln", "gpu_launches": 4 * args.steps, "clocks": sampler.summary()}))
 
 
