@@ -537,20 +537,29 @@ int rms_grid(int64_t rows, int head_dim, int unroll, int sm_count) {
 }
 
 // the kernels are compiled per number of 16-byte chunks in a row (head_dim / 8 = 1..16)
-template <typename T, int C = 16>
+template <typename T, typename Off, int C = 16>
 void rms_launch_fwd(int chunks, bool dual, int grid, cudaStream_t stream, const RmsParams& p) {
   if (chunks == C) {
-    if (dual) rmsnorm_fwd_kernel<T, C, true><<<grid, kRmsThreads, 0, stream>>>(p);
-    else rmsnorm_fwd_kernel<T, C, false><<<grid, kRmsThreads, 0, stream>>>(p);
+    if (dual) rmsnorm_fwd_kernel<T, C, true, Off><<<grid, kRmsThreads, 0, stream>>>(p);
+    else rmsnorm_fwd_kernel<T, C, false, Off><<<grid, kRmsThreads, 0, stream>>>(p);
   } else if constexpr (C > 1) {
-    rms_launch_fwd<T, C - 1>(chunks, dual, grid, stream, p);
+    rms_launch_fwd<T, Off, C - 1>(chunks, dual, grid, stream, p);
   }
 }
 
-template <typename T, int C = 16>
+template <typename T, typename Off, int C = 16>
 void rms_launch_bwd(int chunks, int grid, cudaStream_t stream, const RmsParams& p) {
-  if (chunks == C) rmsnorm_bwd_kernel<T, C><<<grid, kRmsThreads, 0, stream>>>(p);
-  else if constexpr (C > 1) rms_launch_bwd<T, C - 1>(chunks, grid, stream, p);
+  if (chunks == C) rmsnorm_bwd_kernel<T, C, Off><<<grid, kRmsThreads, 0, stream>>>(p);
+  else if constexpr (C > 1) rms_launch_bwd<T, Off, C - 1>(chunks, grid, stream, p);
+}
+
+// every element offset of the tensor fits 31 bits: the kernels can index it with 32-bit arithmetic
+bool rms_small(const dmf_attn_tensor& t, int batch, int seqlen, int heads, int d) {
+  if (t.ptr == nullptr) return true;
+  const __int128 last = static_cast<__int128>(batch - 1) * t.stride_b + static_cast<__int128>(seqlen - 1) * t.stride_l +
+                        static_cast<__int128>(heads - 1) * t.stride_h + d;
+  return last < (static_cast<__int128>(1) << 31) && t.stride_b < (int64_t{1} << 31) && t.stride_l < (int64_t{1} << 31) &&
+         t.stride_h < (int64_t{1} << 31);
 }
 
 int run_rmsnorm_fwd(const dmf_rmsnorm_args* a) {
@@ -576,8 +585,17 @@ int run_rmsnorm_fwd(const dmf_rmsnorm_args* a) {
   p.eps = a->eps;
   const int grid = rms_grid(p.rows, a->head_dim, rms_unroll_fwd(dual), sm_count);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  if (a->dtype == DMF_ATTN_BF16) rms_launch_fwd<__nv_bfloat16>(a->head_dim / 8, dual, grid, stream, p);
-  else rms_launch_fwd<__half>(a->head_dim / 8, dual, grid, stream, p);
+  bool small = true;
+  for (const dmf_attn_tensor* t : {&a->x, &a->tx, &a->y, &a->ty})
+    small = small && rms_small(*t, a->batch, a->seqlen, a->heads, a->head_dim);
+  const int chunks = a->head_dim / 8;
+  if (a->dtype == DMF_ATTN_BF16) {
+    if (small) rms_launch_fwd<__nv_bfloat16, int32_t>(chunks, dual, grid, stream, p);
+    else rms_launch_fwd<__nv_bfloat16, int64_t>(chunks, dual, grid, stream, p);
+  } else {
+    if (small) rms_launch_fwd<__half, int32_t>(chunks, dual, grid, stream, p);
+    else rms_launch_fwd<__half, int64_t>(chunks, dual, grid, stream, p);
+  }
   return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
 }
 
@@ -610,8 +628,17 @@ int run_rmsnorm_bwd(const dmf_rmsnorm_bwd_args* a) {
   p.eps = a->eps;
   const int grid = rms_grid(p.rows, a->head_dim, kRmsUnrollBwd, sm_count);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  if (a->dtype == DMF_ATTN_BF16) rms_launch_bwd<__nv_bfloat16>(a->head_dim / 8, grid, stream, p);
-  else rms_launch_bwd<__half>(a->head_dim / 8, grid, stream, p);
+  bool small = true;
+  for (const dmf_attn_tensor* t : {&a->dy, &a->x, &a->dx})
+    small = small && rms_small(*t, a->batch, a->seqlen, a->heads, a->head_dim);
+  const int chunks = a->head_dim / 8;
+  if (a->dtype == DMF_ATTN_BF16) {
+    if (small) rms_launch_bwd<__nv_bfloat16, int32_t>(chunks, grid, stream, p);
+    else rms_launch_bwd<__nv_bfloat16, int64_t>(chunks, grid, stream, p);
+  } else {
+    if (small) rms_launch_bwd<__half, int32_t>(chunks, grid, stream, p);
+    else rms_launch_bwd<__half, int64_t>(chunks, grid, stream, p);
+  }
   if (cudaGetLastError() != cudaSuccess) return DMF_ATTN_ERR_LAUNCH;
   rmsnorm_dw_reduce_kernel<<<(a->head_dim + 31) / 32, 1024, 0, stream>>>(p.dw_partial, a->dweight, grid, a->head_dim);
   return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;

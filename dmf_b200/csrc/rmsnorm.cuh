@@ -136,13 +136,17 @@ struct RmsPos {
     if (l >= seqlen) { l -= seqlen; ++b; }
     b += d.b;
   }
-  __device__ __forceinline__ int64_t at(int64_t sb, int64_t sl, int64_t sh) const {
-    return static_cast<int64_t>(b) * sb + static_cast<int64_t>(l) * sl + static_cast<int64_t>(h) * sh;
+  // Off = int32_t where the host found every element offset of the launch below 2^31 (one 32-bit multiply-add per
+  // term instead of a 64-bit one: the kernels are bound by instruction issue), else int64_t
+  template <typename Off>
+  __device__ __forceinline__ Off at(int64_t sb, int64_t sl, int64_t sh) const {
+    return static_cast<Off>(b) * static_cast<Off>(sb) + static_cast<Off>(l) * static_cast<Off>(sl) +
+           static_cast<Off>(h) * static_cast<Off>(sh);
   }
 };
 
 // head_dim = 8 * C.  Grid-stride over slices of rms_rows_per_block(C) rows.
-template <typename T, int C, bool kDual>
+template <typename T, int C, bool kDual, typename Off>
 __global__ void __launch_bounds__(kRmsThreads) rmsnorm_fwd_kernel(const RmsParams p) {
   constexpr int R = rms_rows_per_warp(C);
   constexpr int kSlice = R * kRmsWarps;  // rows of one unroll step of the block
@@ -165,7 +169,7 @@ __global__ void __launch_bounds__(kRmsThreads) rmsnorm_fwd_kernel(const RmsParam
   const RmsPos step_rest(stride - kSlice * kRmsUnroll, seqlen, heads);
   for (; wrow < rows; wrow += stride) {
     uint4 xr[kRmsUnroll], tr_[kRmsUnroll];
-    int64_t oy[kRmsUnroll], oty[kRmsUnroll];
+    Off oy[kRmsUnroll], oty[kRmsUnroll];
     bool on[kRmsUnroll];
 #pragma unroll
     for (int u = 0; u < kRmsUnroll; ++u) {
@@ -175,10 +179,10 @@ __global__ void __launch_bounds__(kRmsThreads) rmsnorm_fwd_kernel(const RmsParam
       oy[u] = 0;
       oty[u] = 0;
       if (on[u]) {
-        xr[u] = ld_nc_v4(reinterpret_cast<const T*>(p.x) + pos.at(p.x_sb, p.x_sl, p.x_sh) + col);
-        if constexpr (kDual) tr_[u] = ld_nc_v4(reinterpret_cast<const T*>(p.tx) + pos.at(p.tx_sb, p.tx_sl, p.tx_sh) + col);
-        oy[u] = pos.at(p.y_sb, p.y_sl, p.y_sh) + col;
-        if constexpr (kDual) oty[u] = pos.at(p.ty_sb, p.ty_sl, p.ty_sh) + col;
+        xr[u] = ld_nc_v4(reinterpret_cast<const T*>(p.x) + pos.at<Off>(p.x_sb, p.x_sl, p.x_sh) + col);
+        if constexpr (kDual) tr_[u] = ld_nc_v4(reinterpret_cast<const T*>(p.tx) + pos.at<Off>(p.tx_sb, p.tx_sl, p.tx_sh) + col);
+        oy[u] = pos.at<Off>(p.y_sb, p.y_sl, p.y_sh) + col;
+        if constexpr (kDual) oty[u] = pos.at<Off>(p.ty_sb, p.ty_sl, p.ty_sh) + col;
       }
       pos.advance(step_slice, seqlen, heads);
     }
@@ -213,7 +217,7 @@ __global__ void __launch_bounds__(kRmsThreads) rmsnorm_fwd_kernel(const RmsParam
   }
 }
 
-template <typename T, int C>
+template <typename T, int C, typename Off>
 __global__ void __launch_bounds__(kRmsThreads) rmsnorm_bwd_kernel(const RmsParams p) {
   constexpr int R = rms_rows_per_warp(C);
   constexpr int kSlice = R * kRmsWarps;
@@ -239,7 +243,7 @@ __global__ void __launch_bounds__(kRmsThreads) rmsnorm_bwd_kernel(const RmsParam
   const RmsPos step_rest(stride - kSlice * kRmsUnroll, seqlen, heads);
   for (; wrow < rows; wrow += stride) {
     uint4 xr[kRmsUnroll], gr[kRmsUnroll];
-    int64_t od[kRmsUnroll];
+    Off od[kRmsUnroll];
     bool on[kRmsUnroll];
 #pragma unroll
     for (int u = 0; u < kRmsUnroll; ++u) {
@@ -248,9 +252,9 @@ __global__ void __launch_bounds__(kRmsThreads) rmsnorm_bwd_kernel(const RmsParam
       gr[u] = make_uint4(0u, 0u, 0u, 0u);
       od[u] = 0;
       if (on[u]) {
-        xr[u] = ld_nc_v4(reinterpret_cast<const T*>(p.x) + pos.at(p.x_sb, p.x_sl, p.x_sh) + col);
-        gr[u] = ld_nc_v4(reinterpret_cast<const T*>(p.dy) + pos.at(p.dy_sb, p.dy_sl, p.dy_sh) + col);
-        od[u] = pos.at(p.dx_sb, p.dx_sl, p.dx_sh) + col;
+        xr[u] = ld_nc_v4(reinterpret_cast<const T*>(p.x) + pos.at<Off>(p.x_sb, p.x_sl, p.x_sh) + col);
+        gr[u] = ld_nc_v4(reinterpret_cast<const T*>(p.dy) + pos.at<Off>(p.dy_sb, p.dy_sl, p.dy_sh) + col);
+        od[u] = pos.at<Off>(p.dx_sb, p.dx_sl, p.dx_sh) + col;
       }
       pos.advance(step_slice, seqlen, heads);
     }

@@ -76,6 +76,23 @@ def test_every_row_grouping_and_ragged_row_counts(D, shape):
     assert orc.rel_l2(dw.double().cpu(), dw_ref) < 1e-4
 
 
+def test_offsets_beyond_31_bits_take_the_64_bit_path():
+    """Tensors whose element offsets fit 31 bits are indexed with 32-bit arithmetic; a batch stride of 2^31 + 64
+    elements (a view of a 4.3 GB buffer) must give the same rows through the 64-bit kernels."""
+    L, H, D = 40, 3, 72
+    x, tx, w, dy = _inputs(2, L, H, D, seed=11)
+    stride_b = 2 ** 31 + 64
+    base = torch.empty(stride_b + L * H * D, dtype=torch.bfloat16, device=DEV)
+    big = base.as_strided((2, L, H, D), (stride_b, H * D, D, 1))
+    big.copy_(x.to(DEV))
+    y_big, ty_big = ops.rmsnorm_fwd_raw(big, tx.to(DEV), w.to(DEV), 1e-6)
+    y, ty = ops.rmsnorm_fwd_raw(x.to(DEV), tx.to(DEV), w.to(DEV), 1e-6)
+    assert torch.equal(y_big, y) and torch.equal(ty_big, ty)
+    dx_big, dw_big = ops.rmsnorm_bwd_raw(dy.to(DEV), big, w.to(DEV), 1e-6)
+    dx, dw = ops.rmsnorm_bwd_raw(dy.to(DEV), x.to(DEV), w.to(DEV), 1e-6)
+    assert torch.equal(dx_big, dx) and torch.equal(dw_big, dw)
+
+
 def test_jvp_and_backward_through_the_wrapper_like_the_reference_module():
     """torch.func.jvp through rms_norm vs through the reference's RMSNorm.forward (restated in the oracle),
     both on the GPU in bf16, and the primal gradient vs autograd through the reference form."""
