@@ -139,6 +139,38 @@ def test_block_through_the_wrappers_like_the_reference_block(autocast):
         assert orc.rel_l2(a.float().cpu(), b.float().cpu()) < tol
 
 
+def test_full_size_properties():
+    """At the benchmark's size (64 x 1024 tokens of width 1152), through properties that need no oracle run:
+    the tangent is linear in the input tangents (a factor 2 is exact in every rounding), the dual and plain kernels
+    give the same primal, LayerNorm rows have mean 0 and variance 1, the gradient sums match column sums."""
+    B, L, Cn = 64, 1024, 1152
+    g = torch.Generator(device=DEV).manual_seed(0)
+    rn = lambda *s: torch.randn(*s, device=DEV, generator=g)
+    x, tx = 3.0 * rn(B, L, Cn) + 1.0, rn(B, L, Cn)
+    mods, tmods = (0.3 * rn(B, 1, 6 * Cn)).bfloat16(), (0.1 * rn(B, 1, 6 * Cn)).bfloat16()
+    sh, sc, gt = mods.chunk(6, dim=-1)[:3]
+    tsh, tsc, tgt = tmods.chunk(6, dim=-1)[:3]
+    y, ty = adaln.ln_modulate_fwd_raw(x, tx, sh, sc, tsh, tsc, 1e-6, BF16)
+    y2, ty2 = adaln.ln_modulate_fwd_raw(x, 2 * tx, sh, sc, 2 * tsh, 2 * tsc, 1e-6, BF16)
+    assert torch.equal(y2, y) and torch.equal(ty2, 2 * ty)
+    assert torch.equal(adaln.ln_modulate_fwd_raw(x, None, sh, sc, None, None, 1e-6, BF16)[0], y)
+    zero = torch.zeros_like(mods[..., :Cn])
+    n, _ = adaln.ln_modulate_fwd_raw(x, None, zero, zero, None, None, 1e-6, F32)
+    assert float(n.mean(-1).abs().max()) < 1e-5 and float((n.var(-1, unbiased=False) - 1).abs().max()) < 1e-4
+    h, th = rn(B, L, Cn).bfloat16(), rn(B, L, Cn).bfloat16()
+    out, tout = adaln.gate_residual_fwd_raw(x, tx, h, th, gt, tgt)
+    out2, tout2 = adaln.gate_residual_fwd_raw(x, 2 * tx, h, 2 * th, gt, 2 * tgt)
+    assert torch.equal(out2, out) and torch.equal(tout2, 2 * tout)
+    dy = rn(B, L, Cn).bfloat16()
+    dx, dshift, dscale = adaln.ln_modulate_bwd_raw(dy, x, sc, 1e-6)
+    assert orc.rel_l2(dshift.double(), dy.double().sum(1)) < 1e-6
+    assert orc.rel_l2(dscale.double(), (dy.double() * n.double()).sum(1)) < 1e-5
+    assert float(dx.mean(-1).abs().max()) < 1e-4                      # a LayerNorm gradient has zero row mean
+    dh, dgate = adaln.gate_residual_bwd_raw(x, h, gt)
+    assert orc.rel_l2(dgate.double(), (x.double() * h.double()).sum(1)) < 1e-6
+    assert torch.equal(dh, (gt.float() * x).to(BF16))
+
+
 def test_rejects_what_the_kernels_do_not_cover():
     c = _inputs(1, 8, 384, F32, BF16, BF16)
     with pytest.raises(RuntimeError):
