@@ -93,6 +93,31 @@ def test_offsets_beyond_31_bits_take_the_64_bit_path():
     assert torch.equal(dx_big, dx) and torch.equal(dw_big, dw)
 
 
+def test_full_size_properties():
+    """At the benchmark's size (q and k views of a packed 64 x 1024 x 3 x 16 x 72 projection): the tangent is linear
+    in the input tangent (a factor 2 is exact in every rounding), dual and plain kernels give the same primal, rows
+    have unit mean square for a unit weight, and dweight matches a column sum."""
+    B, L, H, D = 64, 1024, 16, 72
+    g = torch.Generator(device=DEV).manual_seed(0)
+    qkv = torch.randn(B, L, 3, H, D, device=DEV, generator=g).bfloat16()
+    tqkv = (0.1 * torch.randn(B, L, 3, H, D, device=DEV, generator=g)).bfloat16()
+    w = torch.ones(D, device=DEV)
+    for i in (0, 1):
+        x, tx = qkv[:, :, i], tqkv[:, :, i]
+        y, ty = ops.rmsnorm_fwd_raw(x, tx, w, 1e-6)
+        y2, ty2 = ops.rmsnorm_fwd_raw(x, 2 * tx, w, 1e-6)
+        assert torch.equal(y2, y) and torch.equal(ty2, 2 * ty)
+        assert torch.equal(ops.rmsnorm_fwd_raw(x, None, w, 1e-6)[0], y)
+        assert float((y.float().square().mean(-1) - 1).abs().max()) < 1e-2      # bf16 rounding of 72 values
+        assert float((y.float() * ty.float()).mean(-1).abs().max()) < 2e-2        # the tangent is orthogonal to the row
+    dy = torch.randn(B, L, H, D, device=DEV, generator=g).bfloat16()
+    x = qkv[:, :, 0]
+    dx, dw = ops.rmsnorm_bwd_raw(dy, x, w, 1e-6)
+    r = torch.rsqrt(x.double().square().mean(-1, keepdim=True) + 1e-6)
+    assert orc.rel_l2(dw.double(), (dy.double() * x.double() * r).sum((0, 1, 2))) < 1e-5
+    assert float((dx.float() * x.float()).mean(-1).abs().max()) < 5e-2            # dx is orthogonal to x (weight 1)
+
+
 def test_jvp_and_backward_through_the_wrapper_like_the_reference_module():
     """torch.func.jvp through rms_norm vs through the reference's RMSNorm.forward (restated in the oracle),
     both on the GPU in bf16, and the primal gradient vs autograd through the reference form."""
