@@ -140,3 +140,26 @@ def test_adaln_entry_points_reject_bad_arguments_without_a_gpu():
     b.dout, b.h, b.dh = (_lib.Rows(fake, 16 * 768, 768) for _ in range(3))
     b.gate, b.dgate = _lib.Mod(fake, 768), fake
     assert lib.dmf_gate_residual_bwd(C.byref(b)) == 11       # no workspace
+
+
+def test_python_surface_has_no_cpu_path():
+    """Every op of the package raises on CPU tensors instead of computing somewhere else."""
+    import torch
+    from dmf_b200 import adaln, flash_attn_func, flash_attn_qkvpacked_func
+    from dmf_b200.rms_norm import rms_norm
+    q = torch.randn(1, 128, 2, 64).bfloat16()
+    with pytest.raises(Exception):
+        flash_attn_func(q, q, q)
+    with pytest.raises(Exception):
+        flash_attn_qkvpacked_func(torch.stack([q, q, q], dim=2))
+    with pytest.raises(ValueError):
+        flash_attn_qkvpacked_func(q)                       # not a (B, L, 3, H, D) tensor
+    with pytest.raises(Exception):
+        rms_norm(q, torch.ones(64))
+    x = torch.randn(2, 8, 384)
+    mod = torch.zeros(2, 1, 384)
+    assert not adaln.usable(x)
+    with pytest.raises(RuntimeError):
+        adaln.ln_modulate(x, mod, mod)
+    with pytest.raises(RuntimeError):
+        adaln.gate_residual(x, mod, x)
