@@ -634,7 +634,8 @@ def run_model(args):
     steps = args.steps if args.steps != 50 else (5 if args.workload == "C4" else 10)
 
     if args.workload == "C4":
-        global_batch, mb = 256, args.micro_batch
+        global_batch = 256
+        mb = args.micro_batch or next(m for m in (128, 64, 32, 16, 8, 4, 2, 1) if (global_batch // world) % m == 0)
         assert global_batch % (mb * world) == 0, "256 must be divisible by micro_batch * n_gpus"
         n_micro = global_batch // (mb * world)
         st = T.build_train_state(dev, name=args.model, input_size=32, dmf_depth=20, attn_func="fa3", seed=0,
@@ -737,7 +738,9 @@ def main():
     ap.add_argument("--workload", choices=list(WORKLOADS) + ["C4", "C5"], default="C3",
                     help="C3/C2: attention JVP op (default C3, the bench line); C4: DMFT-XL/2 training step, "
                          "global batch 256; C5: DMFT-XL/2 4-step Euler sampling at 512px, 64 images per GPU")
-    ap.add_argument("--micro-batch", type=int, default=32, help="C4: images per forward/backward pass")
+    ap.add_argument("--micro-batch", type=int, default=0,
+                    help="C4: images per forward/backward pass; 0 = the largest of 128, 64, 32 that divides the per-GPU "
+                         "share of the global batch (128 images keep 123 GB of the 180 GB HBM in use)")
     ap.add_argument("--model", default="DMFT-XL/2", help="C4/C5: harness model name (smaller ones for smoke runs)")
     ap.add_argument("--no-graphs", action="store_true", help="C4 / C5: eager launches (and DDP) instead of the CUDA-graphed micro-step / sampler loop")
     ap.add_argument("--op", choices=["dual", "fwd", "bwd", "rmsnorm", "adaln"], default="dual",
