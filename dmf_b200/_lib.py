@@ -26,6 +26,7 @@ EXPORTS = (
     "dmf_attn_abi_version", "dmf_attn_status_string", "dmf_attn_fwd_dual", "dmf_attn_fwd",
     "dmf_attn_bwd", "dmf_attn_bwd_static", "dmf_attn_bwd_workspace_bytes", "dmf_attn_check_status_word",
     "dmf_attn_validate_fwd", "dmf_attn_validate_bwd",
+    "dmf_attn_fwd_dual_f32out", "dmf_attn_selftest_wait_limit", "dmf_attn_kernel_name",
     "dmf_rmsnorm_fwd", "dmf_rmsnorm_bwd", "dmf_rmsnorm_bwd_workspace_bytes",
     "dmf_ln_modulate_fwd", "dmf_ln_modulate_bwd", "dmf_adaln_bwd_workspace_bytes",
     "dmf_gate_residual_fwd", "dmf_gate_residual_bwd",
@@ -152,7 +153,11 @@ def load() -> C.CDLL:
         lib.dmf_attn_abi_version.restype = C.c_int
         lib.dmf_attn_status_string.restype = C.c_char_p
         lib.dmf_attn_status_string.argtypes = [C.c_int]
-        for name in ("dmf_attn_fwd_dual", "dmf_attn_fwd"):
+        lib.dmf_attn_selftest_wait_limit.restype = C.c_int
+        lib.dmf_attn_selftest_wait_limit.argtypes = [C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.dmf_attn_kernel_name.restype = C.c_int
+        lib.dmf_attn_kernel_name.argtypes = [C.c_int32] * 5 + [C.c_char_p, C.c_size_t]
+        for name in ("dmf_attn_fwd_dual", "dmf_attn_fwd", "dmf_attn_fwd_dual_f32out"):
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(FwdArgs)]
@@ -186,6 +191,14 @@ def load() -> C.CDLL:
             raise ImportError(f"libdmf_attn.so has ABI version {got}, this package expects {ABI_VERSION}")
         _lib = lib
         return lib
+
+
+def kernel_name(op: str, seqlen_q: int, seqlen_kv: int, head_dim: int, dtype: int = BF16) -> str:
+    """The kernel template instance the launcher picks for this problem (op: 'dual', 'fwd' or 'bwd')."""
+    buf = C.create_string_buffer(256)
+    check(load().dmf_attn_kernel_name({"dual": 0, "fwd": 1, "bwd": 2}[op], seqlen_q, seqlen_kv, head_dim, dtype,
+                                      buf, len(buf)))
+    return buf.value.decode()
 
 
 def check(status: int) -> None:

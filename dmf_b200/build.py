@@ -6,6 +6,7 @@ no Python or torch dependency.  ``python -m dmf_b200.build`` builds it by hand.
 
 from __future__ import annotations
 
+import fcntl
 import os
 import shutil
 import subprocess
@@ -41,21 +42,37 @@ def _stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources."""
+    """Compile the library if it is missing or older than its sources.
+
+    Several processes may get here at once (one rank per GPU under torchrun, spawned test workers): the stale
+    check and the compile run under an exclusive lock on a sidecar file, so one process builds and the others
+    wait and then find the library fresh; nvcc writes to a temporary name that is moved onto the library in
+    one step, so nobody ever loads a half-written file.
+    """
     if not force and not _stale():
         return LIB
-    nvcc = find_nvcc()
-    if nvcc is None:
-        raise RuntimeError("nvcc not found: cannot build dmf_b200/libdmf_attn.so")
-    cmd = [nvcc, *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}"]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB), *[str(CSRC / s) for s in SOURCES]]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
-    if verbose:
-        sys.stderr.write(res.stderr)
+    with open(PKG / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not _stale():      # somebody else built it while this process waited
+                return LIB
+            nvcc = find_nvcc()
+            if nvcc is None:
+                raise RuntimeError("nvcc not found: cannot build dmf_b200/libdmf_attn.so")
+            tmp = LIB.with_name(f".{LIB.name}.{os.getpid()}.tmp")
+            cmd = [nvcc, *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "--threads", "0"]
+            if verbose:
+                cmd += ["-Xptxas", "-v"]
+            cmd += ["-o", str(tmp), *[str(CSRC / s) for s in SOURCES]]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                tmp.unlink(missing_ok=True)
+                raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
+            os.replace(tmp, LIB)
+            if verbose:
+                sys.stderr.write(res.stderr)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB
 
 

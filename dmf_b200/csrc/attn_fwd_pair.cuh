@@ -134,7 +134,13 @@ __device__ __forceinline__ void issue_pv_pair(bool leader, uint32_t d_tmem, uint
 // products are issued, the G warps only do the epilogue.  Each softmax warp then has its scheduler to
 // itself and a whole score row per thread (no row-max exchange between warpgroups as in the
 // single-CTA plain forward).
-template <typename T, int TAIL, bool kDual, bool kShort>
+//
+// kF32Out (checking mode, not a production path): o and to leave the kernel as fp32, taken from the
+// accumulators before the rounding to the 16-bit output type, with plain per-row global stores
+// (p.o / p.to are then float tensors; their strides count floats).  Everything up to the epilogue
+// is the same code, so what this mode shows is the error of the accumulation itself: the lazy
+// rescale, the exp2 evaluation and the fp32 sums.
+template <typename T, int TAIL, bool kDual, bool kShort, bool kF32Out = false>
 __global__ void __launch_bounds__(kPairThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
   using TR = PairTraits<TAIL, kShort>;
@@ -587,17 +593,41 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
           else
             return static_cast<uint32_t>(TR::kMainBytes + row * 32 + ((ct ^ ((row >> 2) & 1)) << 4));
         };
-        constexpr int kPasses = (kDual && TR::kOutBufs == 1) ? 2 : 1;
+        constexpr int kPasses = (!kF32Out && kDual && TR::kOutBufs == 1) ? 2 : 1;
 #pragma unroll
         for (int pass = 0; pass < kPasses; ++pass) {
-          const bool do_o = TR::kOutBufs == 2 || pass == 0;
-          const bool do_t = kDual && (TR::kOutBufs == 2 || pass == 1);
+          const bool do_o = kF32Out || TR::kOutBufs == 2 || pass == 0;
+          const bool do_t = kDual && (kF32Out || TR::kOutBufs == 2 || pass == 1);
 #pragma unroll
           for (int c = 0; c < DPAD / 16; ++c) {
             uint32_t a[16], t[16];
             tmem_ld_x16(t_o + c * 16, a);
             if (do_t) tmem_ld_x16(t_o + DPAD + c * 16, t);
             tmem_wait_ld();
+            if constexpr (kF32Out) {
+              // fp32 results straight to global memory, 8 columns (two 16-byte stores) at a time
+              float* go = static_cast<float*>(p.o) + static_cast<int64_t>(b) * p.o_sb + lq * p.o_sl + static_cast<int64_t>(h) * p.o_sh;
+              float* gt = kDual ? static_cast<float*>(p.to) + static_cast<int64_t>(b) * p.to_sb + lq * p.to_sl + static_cast<int64_t>(h) * p.to_sh : nullptr;
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                const int col = pair_head_col<TR>(c * 16 + hh * 8);
+                if (col < p.head_dim) {  // accumulator columns past head_dim hold the zero padding
+                  float fo[8], ft[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    fo[i] = __uint_as_float(a[hh * 8 + i]) * inv_l;
+                    ft[i] = kDual ? fmaf(__uint_as_float(t[hh * 8 + i]), inv_l, -mu_n * fo[i]) : 0.f;
+                  }
+                  *reinterpret_cast<float4*>(go + col) = make_float4(fo[0], fo[1], fo[2], fo[3]);
+                  *reinterpret_cast<float4*>(go + col + 4) = make_float4(fo[4], fo[5], fo[6], fo[7]);
+                  if constexpr (kDual) {
+                    *reinterpret_cast<float4*>(gt + col) = make_float4(ft[0], ft[1], ft[2], ft[3]);
+                    *reinterpret_cast<float4*>(gt + col + 4) = make_float4(ft[4], ft[5], ft[6], ft[7]);
+                  }
+                }
+              }
+              continue;
+            }
             uint32_t po[8], pt[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -623,6 +653,7 @@ attn_fwd_pair_kernel(const __grid_constant__ FwdParams p) {
             tc_fence_before_sync();
             mbar_arrive_warp_cluster(lbar(TR::kBarAccEmpty));
           }
+          if constexpr (kF32Out) continue;  // nothing was staged
           fence_proxy_async_smem();
           named_bar_sync(1, 128);
           if (warp == 6 && lane == 0) {

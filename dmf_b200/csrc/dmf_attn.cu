@@ -108,19 +108,21 @@ inline int check_dims(int batch, int lq, int lkv, int heads, int d, int dtype) {
   return DMF_ATTN_OK;
 }
 
-int validate_fwd(const dmf_attn_fwd_args* a, bool dual) {
+int validate_fwd(const dmf_attn_fwd_args* a, bool dual, int out_elem_bytes = 2) {
   if (a == nullptr) return DMF_ATTN_ERR_NULL;
   int st = check_dims(a->batch, a->seqlen_q, a->seqlen_kv, a->heads, a->head_dim, a->dtype);
   if (st != DMF_ATTN_OK) return st;
   if (a->lse == nullptr) return DMF_ATTN_ERR_NULL;
   if (!std::isfinite(a->softmax_scale)) return DMF_ATTN_ERR_SHAPE;
-  const dmf_attn_tensor* prim[] = {&a->q, &a->k, &a->v, &a->o};
+  const dmf_attn_tensor* prim[] = {&a->q, &a->k, &a->v};
   for (const dmf_attn_tensor* t : prim)
     if ((st = check_tensor(*t, 2)) != DMF_ATTN_OK) return st;
+  if ((st = check_tensor(a->o, out_elem_bytes)) != DMF_ATTN_OK) return st;
   if (dual) {
-    const dmf_attn_tensor* tang[] = {&a->tq, &a->tk, &a->tv, &a->to};
+    const dmf_attn_tensor* tang[] = {&a->tq, &a->tk, &a->tv};
     for (const dmf_attn_tensor* t : tang)
       if ((st = check_tensor(*t, 2)) != DMF_ATTN_OK) return st;
+    if ((st = check_tensor(a->to, out_elem_bytes)) != DMF_ATTN_OK) return st;
   }
   return DMF_ATTN_OK;
 }
@@ -193,10 +195,10 @@ int launch_fwd_tail(const FwdParams& p, int tail, int grid, cudaStream_t stream)
 
 // ---- forward launch, CTA-pair variant (dual pass, head_dim <= 96, even number of query tiles) ----
 
-template <typename T, int TAIL, bool kDual, bool kShort>
+template <typename T, int TAIL, bool kDual, bool kShort, bool kF32Out = false>
 int launch_pair_inst(const FwdParams& p, int clusters, cudaStream_t stream) {
   using TR = PairTraits<TAIL, kShort>;
-  auto kernel = attn_fwd_pair_kernel<T, TAIL, kDual, kShort>;
+  auto kernel = attn_fwd_pair_kernel<T, TAIL, kDual, kShort, kF32Out>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::kSmemBytes) != cudaSuccess) {
     (void)cudaGetLastError();
     return DMF_ATTN_ERR_LAUNCH;
@@ -239,6 +241,18 @@ int launch_pair_tail(const FwdParams& p, int tail, int clusters, cudaStream_t st
   }
 }
 
+// The fp32-output checking mode: bf16, dual pass, head_dim 64 and 65..80 only (what its test covers).
+int launch_pair_f32out(const FwdParams& p, int tail, int clusters, cudaStream_t stream) {
+  const bool is_short = p.seqlen_kv <= kShortMaxBlocks * kBlockKV;
+  switch (tail) {
+    case 0: return launch_pair_inst<__nv_bfloat16, 0, true, false, true>(p, clusters, stream);
+    case 16:
+      return is_short ? launch_pair_inst<__nv_bfloat16, 16, true, true, true>(p, clusters, stream)
+                      : launch_pair_inst<__nv_bfloat16, 16, true, false, true>(p, clusters, stream);
+    default: return DMF_ATTN_ERR_HEAD_DIM;
+  }
+}
+
 // DMF_ATTN_PAIR=0 in the environment keeps the single-CTA kernel (for comparisons).
 bool pair_kernel_enabled() {
   static const bool enabled = [] {
@@ -248,8 +262,13 @@ bool pair_kernel_enabled() {
   return enabled;
 }
 
-int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
-  int st = validate_fwd(a, dual);
+// Which kernel template the launcher picks for a problem; one rule for the launch and for dmf_attn_kernel_name.
+bool fwd_uses_pair(int tail, int seqlen_q) {
+  return tail >= 0 && tail <= 32 && ((seqlen_q / kBlockQ) % 2 == 0) && pair_kernel_enabled();
+}
+
+int run_fwd(const dmf_attn_fwd_args* a, bool dual, bool f32out = false) {
+  int st = validate_fwd(a, dual, f32out ? 4 : 2);
   if (st != DMF_ATTN_OK) return st;
   int sm_count = 0;
   if ((st = device_info(&sm_count)) != DMF_ATTN_OK) return st;
@@ -260,7 +279,8 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
   const int B = a->batch, H = a->heads, D = a->head_dim, Lq = a->seqlen_q, Lk = a->seqlen_kv, dt = a->dtype;
   if ((st = make_map_pair(&p.q_main, &p.q_tail, a->q, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
   // CTA-pair kernel: dual pass, P in its own tensor-memory columns (head_dim <= 96), tiles pair up
-  const bool pair = tail <= 32 && ((Lq / kBlockQ) % 2 == 0) && pair_kernel_enabled();
+  const bool pair = fwd_uses_pair(tail, Lq);
+  if (f32out && !(pair && dual && dt == DMF_ATTN_BF16 && tail <= 16)) return DMF_ATTN_ERR_HEAD_DIM;
   const int k_box_rows = pair ? kBlockKV / 2 : kBlockKV;  // a CTA of a pair loads half of the key rows
   if ((st = make_map_pair(&p.k_main, &p.k_tail, a->k, dt, B, Lk, H, D, tail, k_box_rows)) != DMF_ATTN_OK) return st;
   if ((st = make_map(&p.v_map, a->v, dt, B, Lk, H, D, 32, kBlockKV, CU_TENSOR_MAP_SWIZZLE_64B)) != DMF_ATTN_OK) return st;
@@ -308,16 +328,18 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual) {
     }
   }
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  if (pair || !dual) {  // kernels that write their outputs with TMA stores
+  if ((pair || !dual) && !f32out) {  // kernels that write their outputs with TMA stores
     if ((st = make_map_pair(&p.o_main, &p.o_tail, a->o, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK) return st;
   }
   if (pair) {
-    if (dual && (st = make_map_pair(&p.to_main, &p.to_tail, a->to, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK)
+    if (dual && !f32out &&
+        (st = make_map_pair(&p.to_main, &p.to_tail, a->to, dt, B, Lq, H, D, tail, kBlockQ)) != DMF_ATTN_OK)
       return st;
     p.align_enable[1] = 0;  // the pair kernel's V column order has no room for the 8-column shift
     p.num_tiles /= 2;       // tile pairs
     const int max_clusters = sm_count / 2;
     const int clusters = p.num_tiles < max_clusters ? p.num_tiles : max_clusters;
+    if (f32out) return launch_pair_f32out(p, tail, clusters, stream);
     if (dual)
       return dt == DMF_ATTN_BF16 ? launch_pair_tail<__nv_bfloat16, true>(p, tail, clusters, stream)
                                  : launch_pair_tail<__half, true>(p, tail, clusters, stream);
@@ -408,6 +430,11 @@ int launch_bwd_tail(const BwdParams& p, int tail, int grid, cudaStream_t stream)
   }
 }
 
+void bwd_kernel_name(const char* t, int tail, int /*seqlen_q*/, int /*seqlen_kv*/, char* buf, size_t len) {
+  const char* name = (tail <= 32 && bwd_split_enabled()) ? "attn_bwd_split_kernel" : "attn_bwd_kernel";
+  std::snprintf(buf, len, "%s<%s, TAIL=%d, dQ> + %s<%s, TAIL=%d, dK/dV>", name, t, tail, name, t, tail);
+}
+
 int run_bwd(const dmf_attn_bwd_args* a) {
   int st = validate_bwd(a);
   if (st != DMF_ATTN_OK) return st;
@@ -472,8 +499,7 @@ int run_bwd(const dmf_attn_bwd_args* a) {
 static __device__ __align__(256) float g_bwd_static_scratch[2 * DMF_ATTN_STATIC_MAX_ROWS];
 
 struct StaticScratch {
-  std::atomic<int> ready{0};
-  float* ptr = nullptr;
+  std::atomic<float*> ptr{nullptr};
 };
 StaticScratch g_static_scratch[kMaxDevices];
 
@@ -485,16 +511,17 @@ int static_scratch_ptr(float** out) {
     return DMF_ATTN_ERR_DEVICE;
   }
   StaticScratch& s = g_static_scratch[dev];
-  if (s.ready.load(std::memory_order_acquire) == 0) {
+  float* ptr = s.ptr.load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     void* addr = nullptr;
     if (cudaGetSymbolAddress(&addr, g_bwd_static_scratch) != cudaSuccess || addr == nullptr) {
       (void)cudaGetLastError();
       return DMF_ATTN_ERR_DEVICE;
     }
-    s.ptr = static_cast<float*>(addr);  // every racing first caller computes the same value
-    s.ready.store(1, std::memory_order_release);
+    ptr = static_cast<float*>(addr);  // first callers that race all look up, and store, the same address
+    s.ptr.store(ptr, std::memory_order_release);
   }
-  *out = s.ptr;
+  *out = ptr;
   return DMF_ATTN_OK;
 }
 
@@ -514,6 +541,83 @@ int run_bwd_static(const dmf_attn_bwd_args* a) {
   if ((st = static_scratch_ptr(&scratch)) != DMF_ATTN_OK) return st;
   local.workspace = scratch;
   return run_bwd(&local);
+}
+
+// ---- self-test of the bounded wait ----
+
+constexpr int kRoleSelftest = 900;
+
+// One CTA, two waiting threads.  Thread 0 waits on a barrier that nobody ever arrives on: its wait must run
+// out after `limit_cycles`, record kRoleSelftest + 1 in the status word and raise the CTA's abort flag.
+// Thread 32 waits on a second such barrier with a limit 64 times as long: it must come back early, because
+// it sees the abort flag.  Thread 64 arrives on a third barrier and then waits on it: that wait succeeds.
+// result[0..2]: what the three waits returned; result[3]: cycles thread 0 waited.  The kernel holds no
+// tensor memory and no copy in flight, and returns normally.
+__global__ void selftest_wait_limit_kernel(long long limit_cycles, int32_t* status_word, int32_t* result) {
+  __shared__ __align__(8) uint64_t bars[3];
+  __shared__ int abort_flag_mem;
+  volatile int* abort_flag = &abort_flag_mem;
+  if (threadIdx.x == 0) {
+    abort_flag_mem = 0;
+    for (int i = 0; i < 3; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const long long t0 = clock64();
+    const bool ok = mbar_try_wait(smem_u32(&bars[0]), 0) ||
+                    mbar_wait_slow(smem_u32(&bars[0]), 0, abort_flag, status_word, kRoleSelftest + 1, limit_cycles);
+    const long long dt = clock64() - t0;
+    result[0] = ok ? 1 : 0;
+    result[3] = dt > 0x7fffffffll ? 0x7fffffff : static_cast<int32_t>(dt);
+  } else if (threadIdx.x == 32) {
+    const bool ok = mbar_try_wait(smem_u32(&bars[1]), 0) ||
+                    mbar_wait_slow(smem_u32(&bars[1]), 0, abort_flag, status_word, kRoleSelftest + 2, 64 * limit_cycles);
+    result[1] = ok ? 1 : 0;
+  } else if (threadIdx.x == 64) {
+    mbar_arrive(smem_u32(&bars[2]));
+    const bool ok = mbar_try_wait(smem_u32(&bars[2]), 0) ||
+                    mbar_wait_slow(smem_u32(&bars[2]), 0, abort_flag, status_word, kRoleSelftest + 3, limit_cycles);
+    result[2] = ok ? 1 : 0;
+  }
+}
+
+int run_selftest_wait_limit(int64_t limit_cycles, int32_t* status_word, int32_t* result, void* stream) {
+  if (status_word == nullptr || result == nullptr) return DMF_ATTN_ERR_NULL;
+  // between a few microseconds and the library's own limit: this call must end by itself, quickly
+  if (limit_cycles < 1000 || limit_cycles > 50000000) return DMF_ATTN_ERR_SHAPE;
+  int sm_count = 0;
+  int st = device_info(&sm_count);
+  if (st != DMF_ATTN_OK) return st;
+  selftest_wait_limit_kernel<<<1, 96, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles, status_word, result);
+  return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
+}
+
+// ---- name of the kernel a call would launch ----
+
+int kernel_name(int op, int seqlen_q, int seqlen_kv, int head_dim, int dtype, char* buf, size_t len) {
+  if (buf == nullptr || len == 0) return DMF_ATTN_ERR_NULL;
+  if (dtype != DMF_ATTN_BF16 && dtype != DMF_ATTN_FP16) return DMF_ATTN_ERR_DTYPE;
+  const int tail = tail_of(head_dim);
+  if (tail < 0) return DMF_ATTN_ERR_HEAD_DIM;
+  if (seqlen_q < kBlockQ || seqlen_kv < kBlockKV || seqlen_q % kBlockQ || seqlen_kv % kBlockKV) return DMF_ATTN_ERR_SEQLEN;
+  const char* t = dtype == DMF_ATTN_BF16 ? "bf16" : "fp16";
+  if (op == 0 || op == 1) {
+    const char* kind = op == 0 ? "dual" : "plain";
+    if (fwd_uses_pair(tail, seqlen_q)) {
+      const bool is_short = tail == 16 && seqlen_kv <= kShortMaxBlocks * kBlockKV;
+      std::snprintf(buf, len, "attn_fwd_pair_kernel<%s, TAIL=%d, %s%s> (cta_group::2 cluster pair)", t, tail, kind,
+                    is_short ? ", short" : "");
+    } else {
+      std::snprintf(buf, len, "attn_fwd_kernel<%s, TAIL=%d, %s>", t, tail, kind);
+    }
+    return DMF_ATTN_OK;
+  }
+  if (op == 2) {
+    bwd_kernel_name(t, tail, seqlen_q, seqlen_kv, buf, len);
+    return DMF_ATTN_OK;
+  }
+  return DMF_ATTN_ERR_SHAPE;
 }
 
 // ---- per-head RMS norm (q / k) with tangent, and its backward ----
@@ -675,6 +779,17 @@ DMF_API const char* dmf_attn_status_string(int status) {
 DMF_API int dmf_attn_fwd_dual(const dmf_attn_fwd_args* args) { return run_fwd(args, true); }
 
 DMF_API int dmf_attn_fwd(const dmf_attn_fwd_args* args) { return run_fwd(args, false); }
+
+DMF_API int dmf_attn_fwd_dual_f32out(const dmf_attn_fwd_args* args) { return run_fwd(args, true, true); }
+
+DMF_API int dmf_attn_selftest_wait_limit(int64_t limit_cycles, int32_t* status_word, int32_t* result, void* stream) {
+  return run_selftest_wait_limit(limit_cycles, status_word, result, stream);
+}
+
+DMF_API int dmf_attn_kernel_name(int32_t op, int32_t seqlen_q, int32_t seqlen_kv, int32_t head_dim, int32_t dtype,
+                                 char* buf, size_t len) {
+  return kernel_name(op, seqlen_q, seqlen_kv, head_dim, dtype, buf, len);
+}
 
 DMF_API int dmf_attn_validate_fwd(const dmf_attn_fwd_args* args, int dual) { return validate_fwd(args, dual != 0); }
 

@@ -73,7 +73,8 @@ constexpr long long kWaitLimitCycles = 4000000000ll;
 // The first poll is inlined (a wait that is already satisfied costs one shared-memory
 // round trip); everything else lives in an out-of-line slow path.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                            int32_t* status_word, int32_t code) {
+                                            int32_t* status_word, int32_t code,
+                                            long long limit_cycles = kWaitLimitCycles) {
   uint32_t spins = 0;
   long long t0 = 0;
   while (true) {
@@ -83,7 +84,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
       const long long now = clock64();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitCycles) {
+      } else if (now - t0 > limit_cycles) {
         *abort_flag = 1;
         if (status_word != nullptr) atomicCAS(status_word, 0, code);
         return false;

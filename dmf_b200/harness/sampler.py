@@ -36,6 +36,8 @@ def euler_sampler(model, latents, y, num_steps: int = 4, cfg_scale: float = 1.0,
             d_c, d_u = d.chunk(2)
             d = d_u + cfg_scale * (d_c - d_u)
         x = x + float(t_nxt - t_cur) * d   # a host float64: no host tensor enters the device arithmetic
+    if x.is_cuda and not torch.cuda.is_current_stream_capturing():
+        _ops.poll_device_status(x.device)  # a kernel that gave up a wait is reported at the next call, no sync
     return x
 
 
@@ -64,4 +66,5 @@ class GraphedSampler:
         self.y.copy_(y, non_blocking=True)
         self.graph.replay()
         _ops.launch_count += self.launches
+        _ops.poll_device_status(self.z.device)
         return self.out

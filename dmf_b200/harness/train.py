@@ -12,8 +12,19 @@ With ``graphs=True`` (CUDA only) the forward + backward of a micro-batch is capt
 graph and replayed: eager PyTorch needs about 6300 kernel launches per micro-batch of DMFT-XL/2
 (forward-mode AD decomposes into small kernels) and is bound by the host at ~37 us per launch,
 about twice the GPU time.  Gradients then live in one flat fp32 buffer (each ``p.grad`` is a view
-of it) that the captured backward accumulates into; across ranks it is averaged by a single NCCL
-all-reduce of that buffer after the last micro-batch, in place of the DDP wrapper.
+of it) that the captured backward accumulates into.  Across ranks the buffer is averaged by NCCL in
+place of the DDP wrapper, in one of two ways:
+
+* ``overlap=True`` (default): the buffer is cut into a few contiguous buckets, last parameters
+  first (the order in which backward finishes them).  The graph of a rank's LAST micro-batch carries
+  one all-reduce per bucket on a second stream, each starting as soon as the bucket's last gradient
+  has been accumulated, so the collective runs under the rest of the backward pass (what DDP's
+  bucketed reducer does, train_dmf.py:285-287, captured instead of launched from hooks every step);
+* ``overlap=False``: a single all-reduce of the whole buffer after the last micro-batch.
+
+Either way the mean over ranks is taken by scaling the loss by 1 / world size before backward (a
+power of two on 2, 4, 8 GPUs: exact), not by a pass over the reduced buffer, and the clipping
+coefficient is applied inside the fused AdamW kernel instead of by a pass of its own.
 """
 
 from __future__ import annotations
@@ -53,12 +64,20 @@ class TrainState:
     input_size: int
     graphs: bool = False
     flat_grad: torch.Tensor | None = None   # graphs: all gradients, one buffer
-    graphed: dict | None = None             # graphs: (batch, n_micro) -> GraphedMicroStep
+    graphed: dict | None = None             # graphs: (batch, n_micro, dtype, reduces?) -> GraphedMicroStep
+    overlap: bool = True                    # graphs, world > 1: bucketed all-reduce inside the last micro-batch's graph
+    n_buckets: int = 8
+    bucket_bounds: list | None = None       # [(lo, hi, [parameters])] over flat_grad, in launch order
+    comm_stream: torch.cuda.Stream | None = None
+    pool: object | None = None              # memory pool shared by this state's graphs (they never run concurrently)
+    timing: dict | None = None              # set to {} to have train_step record CUDA events around its phases
+    steps_done: int = 0
 
 
 def build_train_state(device, *, name: str = "DMFT-XL/2", input_size: int = 32, dmf_depth: int = 20,
                       attn_func: str = "fa3", qk_norm: bool = False, seed: int = 0, lr: float = 1e-4,
-                      zero_init: bool = True, graphs: bool = False) -> TrainState:
+                      zero_init: bool = True, graphs: bool = False, overlap: bool = True,
+                      n_buckets: int = 8) -> TrainState:
     torch.manual_seed(seed)  # same initial weights on every rank
     model = build_dmft(name, input_size=input_size, dmf_depth=dmf_depth, use_logvar=True, num_classes=1000,
                        attn_func=attn_func, qk_norm=qk_norm)
@@ -82,37 +101,108 @@ def build_train_state(device, *, name: str = "DMFT-XL/2", input_size: int = 32, 
             p.grad = state.flat_grad[off:off + p.numel()].view_as(p)
             off += p.numel()
         state.graphed = {}
+        state.overlap, state.n_buckets = overlap, n_buckets
+        state.bucket_bounds = _make_buckets(params, n_buckets)
+        state.comm_stream = torch.cuda.Stream(device=device)
+        # the clipping coefficient reaches the fused AdamW kernel as its grad_scale (it divides by it)
+        opt.grad_scale = torch.ones((), dtype=torch.float32, device=device)
     return state
 
 
-class GraphedMicroStep:
-    """loss(x, y) / n_micro and its backward (accumulating into the existing ``p.grad``), captured in a CUDA graph."""
+def _make_buckets(params, n_buckets: int):
+    """Cut the flat gradient buffer into at most ``n_buckets`` contiguous ranges of about equal size, at parameter
+    boundaries, listed from the END of the buffer: backward produces the gradients of the last layers first."""
+    sizes = [p.numel() for p in params]
+    total = sum(sizes)
+    target = -(-total // max(1, n_buckets))
+    bounds, hi, acc, members = [], total, 0, []
+    for p, n in zip(reversed(params), reversed(sizes)):
+        acc += n
+        members.append(p)
+        if acc >= target:
+            bounds.append((hi - acc, hi, members))
+            hi, acc, members = hi - acc, 0, []
+    if members:
+        bounds.append((hi - acc, hi, members))
+    assert bounds[-1][0] == 0 and sum(b[1] - b[0] for b in bounds) == total
+    return bounds
 
-    def __init__(self, state: TrainState, batch: int, n_micro: int, autocast_dtype):
+
+def _world() -> int:
+    return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+
+
+class GraphedMicroStep:
+    """loss(x, y) / (n_micro * world) and its backward (accumulating into the existing ``p.grad``), captured in a CUDA
+    graph.  With ``reduce_in_graph`` the capture also holds the bucketed all-reduce of the flat gradient buffer on the
+    state's second stream (see the module docstring); such a graph is only replayed for a rank's last micro-batch."""
+
+    def __init__(self, state: TrainState, batch: int, n_micro: int, autocast_dtype, reduce_in_graph: bool = False):
         dev, S = state.device, state.input_size
         self.x = torch.zeros(batch, 4, S, S, device=dev)
         self.y = torch.zeros(batch, dtype=torch.long, device=dev)
         self.n_micro, self.autocast_dtype, self.state = n_micro, autocast_dtype, state
+        self.loss_div = float(n_micro * _world())
+        self.reduce_in_graph = reduce_in_graph
         keep = state.flat_grad.clone()
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):        # warm-up outside the capture: lazy initialisations, allocator
             for _ in range(3):
-                self._fwd_bwd()
+                self._fwd_bwd(False)
         torch.cuda.current_stream(dev).wait_stream(side)
+        if reduce_in_graph:                  # NCCL's own lazy set-up (communicator, buffers) outside the capture too
+            dist.all_reduce(torch.zeros(1024, device=dev))
+            torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
         launches0 = _ops.launch_count
-        with torch.cuda.graph(self.graph):
-            self.loss = self._fwd_bwd()
+        with torch.cuda.graph(self.graph, pool=state.pool):
+            self.loss = self._fwd_bwd(reduce_in_graph)
+        if state.pool is None:
+            state.pool = self.graph.pool()
         self.launches = _ops.launch_count - launches0   # kernels of this package inside the graph
         state.flat_grad.copy_(keep)          # the warm-up passes accumulated; the capture itself ran nothing
 
-    def _fwd_bwd(self):
+    def _fwd_bwd(self, reduce_buckets: bool):
         st = self.state
         with torch.autocast(device_type="cuda", dtype=self.autocast_dtype):
             loss, _ = st.loss_fn(st.model, st.model, self.x, self.y)
-        loss = loss.mean() / self.n_micro
-        loss.backward()
+        loss = loss.mean() / self.loss_div
+        if not reduce_buckets:
+            loss.backward()
+            return loss.detach()
+        # Bucketed all-reduce under the backward pass.  A hook on every parameter counts its bucket down once the
+        # gradient has been accumulated; buckets are launched strictly in list order (a bucket that completes early
+        # waits for the ones before it), so every rank issues the same sequence of collectives.
+        main, comm = torch.cuda.current_stream(st.device), st.comm_stream
+        pending = [len(b[2]) for b in st.bucket_bounds]
+        nxt = [0]
+
+        def launch_ready():
+            while nxt[0] < len(pending) and pending[nxt[0]] == 0:
+                lo, hi, _ = st.bucket_bounds[nxt[0]]
+                comm.wait_stream(main)          # inside a capture this forks the graph onto the second stream
+                with torch.cuda.stream(comm):
+                    dist.all_reduce(st.flat_grad[lo:hi])
+                nxt[0] += 1
+
+        handles = []
+        for k, (_, _, members) in enumerate(st.bucket_bounds):
+            for p in members:
+                def hook(_p, k=k):
+                    pending[k] -= 1
+                    launch_ready()
+                handles.append(p.register_post_accumulate_grad_hook(hook))
+        try:
+            loss.backward()
+        finally:
+            for h in handles:
+                h.remove()
+        # parameters that took no part in this loss never fire their hook: whatever is left goes now, in order
+        for k in range(len(pending)):
+            pending[k] = 0
+        launch_ready()
+        main.wait_stream(comm)                  # join: the graph's tail depends on every collective
         return loss.detach()
 
     def __call__(self, x, y):
@@ -123,25 +213,49 @@ class GraphedMicroStep:
         return self.loss
 
 
-def _train_step_graphed(state: TrainState, micro_batches, max_grad_norm, ema_decay, autocast_dtype):
+def _mark(state: TrainState, name: str):
+    """Record a CUDA event under ``name`` when the state collects timings (bench runs); no cost otherwise."""
+    if state.timing is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream(state.device))
+        state.timing.setdefault(name, []).append(ev)
+
+
+def accumulate_graphed(state: TrainState, micro_batches, autocast_dtype=torch.bfloat16):
+    """Forward + backward of every micro-batch (graph replays) and the gradient all-reduce; afterwards
+    ``state.flat_grad`` holds the mean gradient over all micro-batches and ranks.  Returns this rank's mean loss."""
     n = len(micro_batches)
+    world = _world()
     total = None
-    for x, y in micro_batches:
-        key = (x.shape[0], n, autocast_dtype)
+    for i, (x, y) in enumerate(micro_batches):
+        in_graph = world > 1 and state.overlap and i == n - 1
+        key = (x.shape[0], n, autocast_dtype, in_graph)
         step = state.graphed.get(key)
         if step is None:
-            step = state.graphed[key] = GraphedMicroStep(state, x.shape[0], n, autocast_dtype)
-        loss = step(x, y)
-        total = loss.clone() if total is None else total + loss
+            step = state.graphed[key] = GraphedMicroStep(state, x.shape[0], n, autocast_dtype, reduce_in_graph=in_graph)
+        loss = step(x, y) * float(world)        # the graph divides by n_micro * world; report the mean over this rank
+        total = loss if total is None else total + loss
+    _mark(state, "backward_done")
+    if world > 1 and not state.overlap:
+        dist.all_reduce(state.flat_grad)        # one collective for all gradients (already scaled by 1 / world)
+    _mark(state, "allreduce_done")
+    return total
+
+
+def _train_step_graphed(state: TrainState, micro_batches, max_grad_norm, ema_decay, autocast_dtype):
+    _mark(state, "step_start")
+    total = accumulate_graphed(state, micro_batches, autocast_dtype)
     flat = state.flat_grad
-    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-        dist.all_reduce(flat)                                  # one collective for all gradients
-        flat.div_(dist.get_world_size())
-    # clip_grad_norm_ on the flat buffer: scale by min(1, max_norm / (norm + 1e-6)), no host sync
-    flat.mul_(torch.clamp(max_grad_norm / (flat.norm(2) + 1e-6), max=1.0))
+    # clip_grad_norm_ on the flat buffer without a host sync and without a pass of its own: the coefficient
+    # min(1, max_norm / (norm + 1e-6)) goes to the fused AdamW kernel, which divides every gradient by grad_scale
+    coef = torch.clamp(max_grad_norm / (flat.norm(2) + 1e-6), max=1.0)
+    state.opt.grad_scale.copy_(1.0 / coef)
     state.opt.step()
-    flat.zero_()                                               # p.grad stay views of the buffer
+    flat.zero_()                                # p.grad stay views of the buffer
     update_ema(state.ema, state.model, ema_decay)
+    _mark(state, "tail_done")
+    state.steps_done += 1
+    _ops.poll_device_status(state.device)       # a kernel that gave up a wait is reported one step later, no sync
     return total
 
 
@@ -158,6 +272,20 @@ def train_step(state: TrainState, micro_batches, *, max_grad_norm: float = 1.0, 
     through DDP, over ranks.  Returns the mean loss (a device tensor; no host sync)."""
     if state.graphs:
         return _train_step_graphed(state, micro_batches, max_grad_norm, ema_decay, autocast_dtype)
+    total = accumulate_eager(state, micro_batches, autocast_dtype)
+    torch.nn.utils.clip_grad_norm_(state.model.parameters(), max_grad_norm)
+    state.opt.step()
+    state.opt.zero_grad(set_to_none=True)
+    update_ema(state.ema, state.model, ema_decay)
+    state.steps_done += 1
+    if state.device.type == "cuda":
+        _ops.poll_device_status(state.device)
+    return total
+
+
+def accumulate_eager(state: TrainState, micro_batches, autocast_dtype=torch.bfloat16):
+    """The same without graphs: eager launches, gradients in ``p.grad``, averaged over ranks by the DDP wrapper during
+    the last micro-batch's backward.  Returns this rank's mean loss."""
     n = len(micro_batches)
     total = None
     for i, (x, y) in enumerate(micro_batches):
@@ -169,8 +297,4 @@ def train_step(state: TrainState, micro_batches, *, max_grad_norm: float = 1.0, 
             loss = loss.mean() / n
             loss.backward()
         total = loss.detach() if total is None else total + loss.detach()
-    torch.nn.utils.clip_grad_norm_(state.model.parameters(), max_grad_norm)
-    state.opt.step()
-    state.opt.zero_grad(set_to_none=True)
-    update_ema(state.ema, state.model, ema_decay)
     return total

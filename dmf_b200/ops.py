@@ -55,6 +55,35 @@ def check_device_status(device=None) -> None:
         raise _lib.DmfAttnError(st, f"status word = {raw.value} (role*100 + barrier index)")
 
 
+# device index -> [pinned host copy of the status word, event recorded behind the copy, copy in flight?]
+_status_polls: dict[int, list] = {}
+
+
+def poll_device_status(device=None) -> None:
+    """check_device_status without a synchronisation, one call late: every call looks at the value the PREVIOUS
+    call read back (if that copy has finished) and queues a new asynchronous copy of the status word to pinned host
+    memory on the current stream.  Meant for once per optimisation step or sampler call: a kernel that gave up a
+    wait is reported at the next step instead of its output being used silently from then on."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_word(device)
+    slot = _status_polls.get(idx)
+    if slot is None:
+        slot = _status_polls[idx] = [torch.zeros(1, dtype=torch.int32).pin_memory(), torch.cuda.Event(), False]
+    host, ev, pending = slot
+    if pending:
+        if not ev.query():
+            return                      # the previous read-back is still queued behind running work
+        slot[2] = False
+        raw = int(host[0])
+        if raw != 0:
+            w.zero_()
+            raise _lib.DmfAttnError(12, f"status word = {raw} (role*100 + barrier index)")
+    host.copy_(w, non_blocking=True)
+    ev.record(torch.cuda.current_stream(device))
+    slot[2] = True
+
+
 def _prep(x: torch.Tensor) -> torch.Tensor:
     """Make a tensor consumable without changing its values: unit stride on D,
     16-byte aligned base and strides (maybe_contiguous in the reference,

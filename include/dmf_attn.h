@@ -185,6 +185,32 @@ int dmf_attn_bwd_static(const dmf_attn_bwd_args* args);
 int dmf_attn_check_status_word(const int32_t* status_word, void* stream, int32_t* raw);
 
 /*
+ * Checking hooks.  None of them has a counterpart in the reference; they exist so that the library's
+ * own tests can reach behaviour that a normal call cannot show.
+ *
+ * dmf_attn_fwd_dual_f32out: dmf_attn_fwd_dual with args->o and args->to as FLOAT tensors (strides in
+ * floats, 16-byte aligned rows): the accumulators are normalised and stored before the rounding to
+ * the 16-bit output type.  This is how the "fp32-accumulated output" tolerance of the path is
+ * checked (max|a-b| / max|b| <= 1e-3 against an fp64 evaluation that rounds its operands where the
+ * kernel does).  bf16 inputs, head_dim <= 80, an even number of 128-row query tiles; anything else
+ * is DMF_ATTN_ERR_HEAD_DIM.  Slow per-row stores: not a production path.
+ *
+ * dmf_attn_selftest_wait_limit: runs one small kernel in which a thread waits on a barrier that is
+ * never signalled, with a wait limit of limit_cycles SM cycles (1e3 .. 5e7) instead of the
+ * library's ~2 s.  The wait must give up, write 901 to *status_word, and the kernel must return
+ * normally with the context intact.  result: four int32 in device memory, {first wait succeeded
+ * (expect 0), a second thread's longer wait succeeded (expect 0: it sees the abort flag), a wait
+ * on a signalled barrier succeeded (expect 1), cycles the first thread waited}.
+ *
+ * dmf_attn_kernel_name: the kernel template instance the launcher picks for a problem, as text
+ * (op: 0 = fused forward + tangent, 1 = plain forward, 2 = backward).
+ */
+int dmf_attn_fwd_dual_f32out(const dmf_attn_fwd_args* args);
+int dmf_attn_selftest_wait_limit(int64_t limit_cycles, int32_t* status_word, int32_t* result, void* stream);
+int dmf_attn_kernel_name(int32_t op, int32_t seqlen_q, int32_t seqlen_kv, int32_t head_dim, int32_t dtype,
+                         char* buf, size_t len);
+
+/*
  * Argument validation only (no device work): the status the compute entry
  * points would return for these arguments before touching the GPU.
  */

@@ -146,6 +146,60 @@ def attn_jvp_online(q, k, v, tq, tk, tv, softmax_scale: Optional[float] = None,
     return O.transpose(1, 2), dO.transpose(1, 2), lse
 
 
+def attn_jvp_online_lazy(q, k, v, tq, tk, tv, softmax_scale: Optional[float] = None, block_kv: int = 128,
+                         threshold_log2: float = 8.0, emulate_bf16: bool = True, dtype=torch.float64):
+    """The same recurrence with the operand roundings of the sm_100a kernel, evaluated in fp64.
+
+    This is the comparison partner for the kernel's fp32-output checking mode: it rounds where the kernel
+    rounds and nowhere else, so the difference that remains is the kernel's accumulation error.
+
+    * exponents are taken in base 2 relative to a LAZILY updated maximum: the first block sets it to the
+      block's row maximum; afterwards it only moves (to the block's maximum) when that exceeds it by more
+      than ``threshold_log2``, and only then are the running sums rescaled.  bf16 rounding is not invariant
+      under a change of the reference point unless the change is a power of two, so P has to be formed the
+      way the kernel forms it;
+    * l sums the unrounded P; P is then rounded to bf16;
+    * G = bf16(P) * dS (dS carries the softmax scale), mu sums the unrounded G; G is then rounded to bf16;
+    * O += bf16(P) V,  T += bf16(P) dV + bf16(G) V;  o = O / l,  to = T / l - (mu / l) o,
+      lse = ln 2 * (m + log2 l).
+    """
+    d = q.shape[-1]
+    s = d ** -0.5 if softmax_scale is None else softmax_scale
+    Q, K, V, dQ, dK, dV = (x.to(dtype).transpose(1, 2) for x in (q, k, v, tq, tk, tv))
+    B, H, Lq, D = Q.shape
+    Lk = K.shape[2]
+    m = None
+    l = torch.zeros((B, H, Lq), dtype=dtype)
+    mu = torch.zeros((B, H, Lq), dtype=dtype)
+    Oacc = torch.zeros((B, H, Lq, D), dtype=dtype)
+    Tacc = torch.zeros((B, H, Lq, D), dtype=dtype)
+    for j in range(0, Lk, block_kv):
+        Kj, Vj, dKj, dVj = (x[:, :, j:j + block_kv] for x in (K, V, dK, dV))
+        S2 = (s * LOG2E) * (Q @ Kj.transpose(-2, -1))          # scores in log2 units
+        m_blk = S2.amax(-1)
+        if m is None:
+            m = m_blk
+        else:
+            need = m_blk > m + threshold_log2
+            alpha = torch.where(need, torch.exp2(m - m_blk), torch.ones_like(m))
+            m = torch.where(need, m_blk, m)
+            l, mu = l * alpha, mu * alpha
+            Oacc, Tacc = Oacc * alpha[..., None], Tacc * alpha[..., None]
+        P = torch.exp2(S2 - m[..., None])
+        l = l + P.sum(-1)
+        Pr = _round(P, emulate_bf16)
+        dS = s * (dQ @ Kj.transpose(-2, -1) + Q @ dKj.transpose(-2, -1))
+        G = Pr * dS
+        mu = mu + G.sum(-1)
+        Gr = _round(G, emulate_bf16)
+        Oacc = Oacc + Pr @ Vj
+        Tacc = Tacc + Gr @ Vj + Pr @ dVj
+    O = Oacc / l[..., None]
+    dO = Tacc / l[..., None] - (mu / l)[..., None] * O
+    lse = (m + torch.log2(l)) * math.log(2.0)
+    return O.transpose(1, 2), dO.transpose(1, 2), lse
+
+
 def attn_bwd_base(q, k, v, dout):
     """Primal backward through autograd of the 'base' path: (dq, dk, dv)."""
     q, k, v = (x.detach().clone().requires_grad_(True) for x in (q, k, v))

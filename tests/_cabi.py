@@ -88,3 +88,32 @@ def bwd(dout, q, k, v, o, lse, scale=None, expect=0, packed_out=False):
         st2 = lib.dmf_attn_check_status_word(sw.data_ptr(), a.stream, C.byref(raw))
         assert st2 == 0, f"device-side wait gave up: status word {raw.value}"
     return dq, dk, dv, st
+
+
+def fwd_dual_f32out(q, k, v, tq, tk, tv, scale=None, expect=0):
+    """dmf_attn_fwd_dual_f32out: o and to as fp32 tensors (the accumulators before the 16-bit rounding).
+    Returns (o, to, lse, status)."""
+    B, Lq, H, D = q.shape
+    dev = q.device
+    nan = float("nan")
+    o = torch.full((B, Lq, H, D), nan, dtype=torch.float32, device=dev)
+    to = torch.full((B, Lq, H, D), nan, dtype=torch.float32, device=dev)
+    lse = torch.full((B, H, Lq), nan, dtype=torch.float32, device=dev)
+    sw = status_word(dev)
+    a = _lib.FwdArgs()
+    a.batch, a.seqlen_q, a.seqlen_kv, a.heads, a.head_dim = B, Lq, k.shape[1], H, D
+    a.dtype = _DT[q.dtype]
+    a.softmax_scale = float(D ** -0.5 if scale is None else scale)
+    a.q, a.k, a.v, a.o = t4(q), t4(k), t4(v), t4(o)
+    a.tq, a.tk, a.tv, a.to = t4(tq), t4(tk), t4(tv), t4(to)
+    a.lse = lse.data_ptr()
+    a.status_word = sw.data_ptr()
+    a.stream = torch.cuda.current_stream(dev).cuda_stream
+    lib = _lib.load()
+    st = lib.dmf_attn_fwd_dual_f32out(C.byref(a))
+    assert st == expect, f"status {st}: {lib.dmf_attn_status_string(st).decode()}"
+    if st == 0:
+        raw = C.c_int32(0)
+        st2 = lib.dmf_attn_check_status_word(sw.data_ptr(), a.stream, C.byref(raw))
+        assert st2 == 0, f"device-side wait gave up: status word {raw.value}"
+    return o, to, lse, st

@@ -105,3 +105,52 @@ def test_train_step_two_gloo_ranks():
     for rank in range(world):
         finite, moved, same, ema_moved = out[rank]
         assert finite and moved and same and ema_moved
+
+
+def _failing_worker(rank, world, port, out):
+    """Rank 1 fails on the host before the gradient all-reduce (it never enters the step); rank 0 must not hang:
+    its step ends with an exception within the process group's timeout and the group is torn down."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from dmf_b200.harness import train as T
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    dev = torch.device("cpu")
+    st = T.build_train_state(dev, name="DMFT-S/2", input_size=8, dmf_depth=8, attn_func="base", seed=3, zero_init=False)
+    gen = torch.Generator().manual_seed(100 + rank)
+    batches = [T.synthetic_batch(st, 2, generator=gen)]
+    dist.barrier()                      # both ranks are up and the model is wrapped
+    if rank == 1:
+        out[rank] = "raised before the all-reduce"
+        raise RuntimeError("injected host-side failure on rank 1")
+    t0 = time.time()
+    try:
+        T.train_step(st, batches)
+        out[rank] = "no error"
+    except Exception as e:              # gloo: peer closed the connection, or the collective timed out
+        out[rank] = f"error after {time.time() - t0:.1f} s: {type(e).__name__}"
+    try:
+        dist.destroy_process_group()
+        out["teardown"] = "ok"
+    except Exception as e:
+        out["teardown"] = f"failed: {e!r}"
+
+
+def test_a_rank_that_fails_before_the_allreduce_ends_the_other_ranks_step_with_an_error():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    mgr = ctx.Manager()
+    out = mgr.dict()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    assert all(not p.is_alive() for p in procs), "a rank hung"
+    assert procs[1].exitcode != 0                       # the injected failure
+    assert procs[0].exitcode == 0
+    assert out[1] == "raised before the all-reduce"
+    assert out[0].startswith("error after"), out[0]
+    assert float(out[0].split()[2]) < 60.0
+    assert out["teardown"] == "ok"

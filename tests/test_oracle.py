@@ -134,3 +134,21 @@ def test_adaln_closed_forms_match_autodiff_of_the_reference_forms():
     dx, dh, dg = ada.gate_residual_bwd_closed_form(dy, h, gt)
     for got, want in zip([t.grad for t in xs], [dx, dg, dh]):
         assert float((got - want).abs().max()) < 1e-10
+
+
+def test_lazy_rescale_variant_is_the_same_function_and_shows_why_it_exists():
+    """Without rounding, moving the reference point of the exponent lazily changes nothing; with bf16 rounding of P
+    it does, at the size of one bf16 rounding, which is why the fp32-output check of the kernel needs this variant."""
+    q, k, v, tq, tk, tv = orc.make_inputs(1, 512, 2, 72, seed=9, tangent_scale=0.1)
+    # large logits in a few rows, so that the lazy maximum really moves between blocks
+    q[:, :7] *= 6.0
+    o_ref, do_ref, lse_ref = orc.attn_jvp_closed_form(q, k, v, tq, tk, tv)
+    o, do, lse = orc.attn_jvp_online_lazy(q, k, v, tq, tk, tv, emulate_bf16=False)
+    assert orc.max_rel(o, o_ref) < 1e-12 and orc.max_rel(do, do_ref) < 1e-11 and orc.max_rel(lse, lse_ref) < 1e-12
+    o0, do0, _ = orc.attn_jvp_online_lazy(q, k, v, tq, tk, tv, threshold_log2=0.0, emulate_bf16=False)
+    assert orc.max_rel(o0, o_ref) < 1e-12 and orc.max_rel(do0, do_ref) < 1e-11
+    # rounded: both schedules stay within the bf16 floor of the exact result, but differ from each other
+    ob, dob, _ = orc.attn_jvp_online_lazy(q, k, v, tq, tk, tv, emulate_bf16=True)
+    oe, doe, _ = orc.attn_jvp_online(q, k, v, tq, tk, tv, emulate_bf16=True)
+    assert orc.rel_l2(ob, o_ref) < 6e-3 and orc.rel_l2(dob, do_ref) < 6e-3
+    assert 1e-5 < orc.max_rel(ob, oe) < 1e-2
