@@ -431,7 +431,7 @@ def run_ours(args):
     numa_cpus = _pin_to_gpu_numa_node(local_rank)     # before any pinned host buffer is allocated
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=__import__("datetime").timedelta(seconds=900))
 
     from dmf_b200 import ops
 
@@ -576,17 +576,10 @@ def run_ours(args):
     # ---- the whole-model configurations on all N GPUs: C5 (sampling, no collective), C4 (training, all-reduce) ----
     c4 = c5 = None
     if op == "dual" and args.batch is None and not args.no_model:
-        for name in ("C5", "C4"):
-            try:
-                rec = _model_record(args, name, world, rank, dev, steps=None, warm=None)
-            except Exception as e:          # keep the headline line; say what went wrong
-                rec = {"error": f"{type(e).__name__}: {e}"[:500]}
-            if name == "C4":
-                c4 = rec
-            else:
-                c5 = rec
-            gc.collect()
-            torch.cuda.empty_cache()
+        c5 = _model_record_in_children(args, "C5", world, rank, local_rank, 1)
+        sync_all()
+        c4 = _model_record_in_children(args, "C4", world, rank, local_rank, 2)
+        sync_all()
 
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and op == "dual":
@@ -1073,6 +1066,42 @@ def _model_record(args, workload, world, rank, dev, steps=None, warm=None):
     return rec
 
 
+def _model_record_in_children(args, workload, world, rank, local_rank, port_offset, limit_s=420):
+    """A whole-model configuration for the default line, run as a job of its own: every rank of this job starts one
+    child process (`bench.py --workload C4|C5 --record-only`), the children form their own process group on another
+    port, and rank 0's child prints the record.  A failure or a stall in there costs the sub-record (the child is
+    ended when its time limit runs out), never the headline of this process."""
+    cmd = [sys.executable, str(ROOT / "bench.py"), "--workload", workload, "--gpus", str(world), "--record-only",
+           "--model", args.model, "--buckets", str(args.buckets)]
+    if args.no_graphs:
+        cmd.append("--no-graphs")
+    if args.no_overlap:
+        cmd.append("--no-overlap")
+    if args.micro_batch:
+        cmd += ["--micro-batch", str(args.micro_batch)]
+    env = dict(os.environ)
+    env["MASTER_ADDR"] = "127.0.0.1"
+    env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 16 + port_offset)
+    env["RANK"], env["LOCAL_RANK"], env["WORLD_SIZE"] = str(rank), str(local_rank), str(world)
+    for k in ("TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT", "TORCHELASTIC_MAX_RESTARTS", "GROUP_RANK",
+              "ROLE_RANK", "TORCHELASTIC_USE_AGENT_STORE"):
+        env.pop(k, None)
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=limit_s, env=env)
+    except subprocess.TimeoutExpired:     # subprocess.run has ended the child it started
+        return {"error": f"the {workload} child process did not finish within {limit_s} s"}
+    if rank != 0:
+        return None
+    for line in reversed(res.stdout.strip().splitlines()):
+        try:
+            rec = json.loads(line)
+        except ValueError:
+            continue
+        if isinstance(rec, dict) and "metric" in rec:
+            return rec
+    return {"error": f"child exited {res.returncode}: {(res.stderr or res.stdout).strip()[-600:]}"}
+
+
 def run_model(args):
     """--workload C4 / C5 as the bench line itself."""
     import torch
@@ -1088,10 +1117,13 @@ def run_model(args):
     _pin_to_gpu_numa_node(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        # a collective that cannot complete ends the job with an error after three minutes instead of blocking it
+        dist.init_process_group("nccl", device_id=dev, timeout=__import__("datetime").timedelta(seconds=180))
     rec = _model_record(args, args.workload, world, rank, dev,
                         steps=None if args.steps == 50 else args.steps, warm=None if args.warmup == 10 else args.warmup)
-    if rank == 0:
+    if rank == 0 and args.record_only:
+        print(json.dumps(rec), flush=True)
+    elif rank == 0:
         line = {
             "metric": rec["metric"], "value": rec["value"], "unit": rec["unit"], "n_gpus": world, "steps": rec["steps"],
             "warmup": rec["warmup"], "ms_per_step": rec["ms_per_step"], "higher_is_better": True,
@@ -1136,6 +1168,8 @@ def main():
     ap.add_argument("--op-only", action="store_true",
                     help="only the timed op and its roofline: no sustained loop, host-buffer leg, CPU baseline, secondary "
                          "kernels, comparator or whole-model records (profiling runs)")
+    ap.add_argument("--record-only", action="store_true",
+                    help="C4 / C5: print the bare record (what the default line embeds as its c4 / c5 entry)")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="chunks along the batch of the pipelined host-buffer leg")
     ap.add_argument("--no-overlap", action="store_true",
                     help="C4: one all-reduce after the last micro-batch instead of bucketed all-reduces inside its graph")

@@ -13,6 +13,7 @@
 #include <cstring>
 
 #include "attn_bwd.cuh"
+#include "attn_bwd_fused.cuh"
 #include "attn_bwd_split.cuh"
 #include "attn_fwd.cuh"
 #include "attn_fwd_pair.cuh"
@@ -430,7 +431,83 @@ int launch_bwd_tail(const BwdParams& p, int tail, int grid, cudaStream_t stream)
   }
 }
 
-void bwd_kernel_name(const char* t, int tail, int /*seqlen_q*/, int /*seqlen_kv*/, char* buf, size_t len) {
+// ---- backward in one pass (two-tile sequences, head_dim <= 80) ----
+
+// DMF_ATTN_BWD_FUSED=0 in the environment keeps the two-launch backward (for comparisons).
+bool bwd_fused_enabled() {
+  static const bool enabled = [] {
+    const char* e = std::getenv("DMF_ATTN_BWD_FUSED");
+    return e == nullptr || e[0] != '0';
+  }();
+  return enabled;
+}
+
+bool bwd_uses_fused(int tail, int seqlen_q, int seqlen_kv) {
+  return tail >= 0 && tail <= 16 && seqlen_q == kBwdFusedSeqlen && seqlen_kv == kBwdFusedSeqlen && bwd_fused_enabled();
+}
+
+template <typename T, int TAIL>
+int launch_bwd_fused_inst(const BwdFusedParams& p, int clusters, cudaStream_t stream) {
+  using TR = BwdFusedTraits<TAIL>;
+  auto kernel = attn_bwd_fused_kernel<T, TAIL>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::kSmemBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_LAUNCH;
+  }
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(kBwdFusedThreads, 1, 1);
+  cfg.dynamicSmemBytes = TR::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_LAUNCH;
+  }
+  return DMF_ATTN_OK;
+}
+
+int run_bwd_fused(const dmf_attn_bwd_args* a, int tail, int sm_count) {
+  const int B = a->batch, H = a->heads, D = a->head_dim, L = a->seqlen_q, dt = a->dtype;
+  BwdFusedParams p;
+  std::memset(&p, 0, sizeof(p));
+  int st;
+  if ((st = make_map_pair(&p.q_main, &p.q_tail, a->q, dt, B, L, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.do_main, &p.do_tail, a->dout, dt, B, L, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.k_main, &p.k_tail, a->k, dt, B, L, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.v_main, &p.v_tail, a->v, dt, B, L, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.o_main, &p.o_tail, a->o, dt, B, L, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.dq_main, &p.dq_tail, a->dq, dt, B, L, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.dk_main, &p.dk_tail, a->dk, dt, B, L, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  if ((st = make_map_pair(&p.dv_main, &p.dv_tail, a->dv, dt, B, L, H, D, tail, 128)) != DMF_ATTN_OK) return st;
+  p.lse = a->lse;
+  p.status_word = a->status_word;
+  p.batch = B; p.heads = H; p.head_dim = D;
+  p.num_heads_total = B * H;
+  p.scale = a->softmax_scale;
+  p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
+  const int max_clusters = sm_count / 2;
+  const int clusters = p.num_heads_total < max_clusters ? p.num_heads_total : max_clusters;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (dt == DMF_ATTN_BF16)
+    return tail == 0 ? launch_bwd_fused_inst<__nv_bfloat16, 0>(p, clusters, stream)
+                     : launch_bwd_fused_inst<__nv_bfloat16, 16>(p, clusters, stream);
+  return tail == 0 ? launch_bwd_fused_inst<__half, 0>(p, clusters, stream)
+                   : launch_bwd_fused_inst<__half, 16>(p, clusters, stream);
+}
+
+void bwd_kernel_name(const char* t, int tail, int seqlen_q, int seqlen_kv, char* buf, size_t len) {
+  if (bwd_uses_fused(tail, seqlen_q, seqlen_kv)) {
+    std::snprintf(buf, len, "attn_bwd_fused_kernel<%s, TAIL=%d> (one pass, cluster of two CTAs per head)", t, tail);
+    return;
+  }
   const char* name = (tail <= 32 && bwd_split_enabled()) ? "attn_bwd_split_kernel" : "attn_bwd_kernel";
   std::snprintf(buf, len, "%s<%s, TAIL=%d, dQ> + %s<%s, TAIL=%d, dK/dV>", name, t, tail, name, t, tail);
 }
@@ -443,6 +520,9 @@ int run_bwd(const dmf_attn_bwd_args* a) {
   const int tail = tail_of(a->head_dim);
   const int B = a->batch, H = a->heads, D = a->head_dim, Lq = a->seqlen_q, Lk = a->seqlen_kv, dt = a->dtype;
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  // two-tile sequences: the one-pass kernel (it needs no workspace; lse rows are fetched with 16-byte bulk copies)
+  if (bwd_uses_fused(tail, Lq, Lk) && (reinterpret_cast<uintptr_t>(a->lse) & 15u) == 0)
+    return run_bwd_fused(a, tail, sm_count);
 
   BwdParams p;
   std::memset(&p, 0, sizeof(p));
@@ -785,6 +865,17 @@ DMF_API int dmf_attn_fwd_dual_f32out(const dmf_attn_fwd_args* args) { return run
 DMF_API int dmf_attn_selftest_wait_limit(int64_t limit_cycles, int32_t* status_word, int32_t* result, void* stream) {
   return run_selftest_wait_limit(limit_cycles, status_word, result, stream);
 }
+
+#ifdef DMF_TRACE
+// diagnostic builds only: copy the in-kernel timeline of the one-pass backward out (see attn_bwd_fused.cuh)
+DMF_API int dmf_trace_read_bwd_fused(unsigned long long* out, size_t count) {
+  const size_t have = sizeof(g_bwd_fused_trace) / sizeof(unsigned long long);
+  if (cudaDeviceSynchronize() != cudaSuccess) return DMF_ATTN_ERR_DEVICE;
+  if (cudaMemcpyFromSymbol(out, g_bwd_fused_trace, sizeof(unsigned long long) * (count < have ? count : have)) != cudaSuccess)
+    return DMF_ATTN_ERR_DEVICE;
+  return DMF_ATTN_OK;
+}
+#endif
 
 DMF_API int dmf_attn_kernel_name(int32_t op, int32_t seqlen_q, int32_t seqlen_kv, int32_t head_dim, int32_t dtype,
                                  char* buf, size_t len) {

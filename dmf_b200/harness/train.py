@@ -151,8 +151,12 @@ class GraphedMicroStep:
             for _ in range(3):
                 self._fwd_bwd(False)
         torch.cuda.current_stream(dev).wait_stream(side)
-        if reduce_in_graph:                  # NCCL's own lazy set-up (communicator, buffers) outside the capture too
-            dist.all_reduce(torch.zeros(1024, device=dev))
+        if reduce_in_graph:
+            # NCCL sets a transport up the first time a collective needs it (which one depends on the message size):
+            # that involves allocations and a handshake between the ranks, neither of which may happen inside a
+            # capture.  So every bucket is all-reduced once here, at its real size (flat_grad is restored below).
+            for lo, hi, _ in state.bucket_bounds:
+                dist.all_reduce(state.flat_grad[lo:hi])
             torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
         launches0 = _ops.launch_count

@@ -20,10 +20,13 @@ pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
 
 # Tolerance of the fp32-accumulated outputs, as max|a - b| / max|b| against the fp64 evaluation with the same
-# operand roundings (bf16 inputs, bf16 P, bf16 P*dS).  What is left is the kernel's own arithmetic: fp32 sums,
-# the exp2 evaluation (a quarter of the exponentials use a cubic with 7.5e-5 relative error, which moves about one
-# P element in 200 by one bf16 step) and the fp32 rescaling.
+# operand roundings (bf16 inputs, bf16 P, bf16 P*dS).  What is left is the kernel's own arithmetic: fp32 sums, fp32
+# rescaling, and the few P or P*dS elements (about one in 10^4) that an fp32 exponent argument and ex2.approx put
+# on the other side of a bf16 rounding boundary than the fp64 evaluation; one such element of a heavy key is worth
+# up to a few 1e-4 in this max-norm metric, which is why the observed values sit near 1e-4 and not near 1e-6.
 TOL_F32_OUT = 1e-3
+# the same comparison in relative L2, where isolated rounding flips do not dominate
+TOL_F32_OUT_L2 = 3e-4
 
 
 @pytest.mark.parametrize("B,L,H,D,qk_norm,big_rows", [
@@ -36,7 +39,7 @@ TOL_F32_OUT = 1e-3
 def test_fp32_accumulated_outputs_within_1e_3(B, L, H, D, qk_norm, big_rows):
     ins = orc.make_inputs(B, L, H, D, seed=31 + D + L, tangent_scale=0.1, qk_norm=qk_norm)
     if big_rows:
-        ins[0][:, 5:37] *= 5.0           # rows with large logits: the lazily updated maximum moves between blocks
+        ins[0][:, 5:37] *= 8.0           # rows with large logits: the lazily updated maximum moves between blocks
     dev_in = [x.bfloat16().to(DEV) for x in ins]
     o, to, lse, _ = _cabi.fwd_dual_f32out(*dev_in)
     assert o.dtype == torch.float32 and not torch.isnan(o).any() and not torch.isnan(to).any()
@@ -44,11 +47,15 @@ def test_fp32_accumulated_outputs_within_1e_3(B, L, H, D, qk_norm, big_rows):
     o_ref, to_ref, lse_ref = orc.attn_jvp_online_lazy(*ref_in, emulate_bf16=True)
     e_o, e_to = orc.max_rel(o.cpu(), o_ref), orc.max_rel(to.cpu(), to_ref)
     e_lse = orc.max_rel(lse.cpu(), lse_ref)
-    print(f"fp32-out D={D} L={L}: max-rel o {e_o:.2e} to {e_to:.2e} lse {e_lse:.2e}")
+    l2_o, l2_to = orc.rel_l2(o.cpu(), o_ref), orc.rel_l2(to.cpu(), to_ref)
+    print(f"fp32-out D={D} L={L} qk_norm={qk_norm} big_rows={big_rows}: max-rel o {e_o:.2e} to {e_to:.2e} "
+          f"lse {e_lse:.2e}; rel-L2 o {l2_o:.2e} to {l2_to:.2e}")
     assert e_o <= TOL_F32_OUT and e_to <= TOL_F32_OUT and e_lse <= TOL_F32_OUT
-    # the 16-bit entry point gives the rounding of these very values
-    o16, to16, _, _ = _cabi.fwd(*dev_in)
-    assert torch.equal(o16, o.to(torch.bfloat16)) and torch.equal(to16, to.to(torch.bfloat16))
+    assert l2_o <= TOL_F32_OUT_L2 and l2_to <= TOL_F32_OUT_L2
+    # the 16-bit entry point computes the same thing up to its own output rounding (and its faster exponentials)
+    o16, to16, lse16, _ = _cabi.fwd(*dev_in)
+    assert orc.rel_l2(o16.float(), o) < 4e-3 and orc.rel_l2(to16.float(), to) < 4e-3
+    assert orc.max_rel(lse16, lse) < 1e-4
 
 
 def test_fp32_out_rejects_what_it_does_not_cover():

@@ -3,8 +3,10 @@ last micro-batch's graph, the graphed step with one all-reduce after it, and the
 (what the reference runs, train_dmf.py:285-287, 330) must produce the same averaged gradients, and every rank must
 hold the same parameters after an optimisation step.  Needs two GPUs; skipped otherwise."""
 
+import datetime
 import os
 import socket
+import traceback
 from functools import partial
 
 import pytest
@@ -30,7 +32,8 @@ def _worker(rank, world, port, out):
     from dmf_b200.harness import train as T
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    # a collective that cannot complete ends with an error after a minute instead of blocking the test
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=60))
     try:
         gen = torch.Generator(device=dev).manual_seed(5 + rank)      # every rank has its own data and noise
         eps = torch.randn(4, 4, 32, 32, device=dev, generator=gen)
@@ -39,9 +42,13 @@ def _worker(rank, world, port, out):
 
         def fixed_loss(model, raw, x, y):    # the DMF loss with its random draws fixed (a captured graph owns its RNG offsets)
             x_t, v = (1 - t) * x + t * eps, eps - x
+            # flow-matching term through `model` (the DDP wrapper in the eager mode: its forward is what arms the
+            # gradient reducer), MeanFlow term through the raw module under torch.func.jvp, as DMFLoss does
+            v_fm, _ = model(x_t, t, t, y, return_logvar=True)
             (u, _), (du, _) = torch.func.jvp(partial(raw, y=y, return_logvar=True), (x_t, t, r),
                                              (v, torch.ones_like(t), torch.zeros_like(r)))
-            return ((u - (v + (r - t) * du).detach()) ** 2).mean(dim=(1, 2, 3)), {}
+            fm = ((v_fm - v) ** 2).mean(dim=(1, 2, 3))
+            return 0.5 * (fm + ((u - (v + (r - t) * du).detach()) ** 2).mean(dim=(1, 2, 3))), {}
 
         grads, losses = {}, {}
         for mode in ("overlap", "single", "ddp"):
@@ -82,8 +89,12 @@ def _worker(rank, world, port, out):
         res["loss_finite"] = bool(torch.isfinite(loss))
         ops.check_device_status(dev)
         out[rank] = res
-    finally:
-        dist.destroy_process_group()
+    except BaseException:
+        # report, and leave without tearing the process group down: after a failure in the middle of a sequence of
+        # collectives the teardown itself can block on the other rank
+        out[rank] = {"error": traceback.format_exc()}
+        os._exit(1)
+    dist.destroy_process_group()
 
 
 def test_graphed_allreduce_matches_ddp_on_two_gpus():
@@ -97,8 +108,14 @@ def test_graphed_allreduce_matches_ddp_on_two_gpus():
     for p in procs:
         p.start()
     for p in procs:
-        p.join(timeout=600)
-    assert all(not p.is_alive() for p in procs), "a rank hung"
+        p.join(timeout=200)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:                      # never leave a rank behind on the GPU
+        p.terminate()
+        p.join(timeout=30)
+    errors = {r: out[r]["error"] for r in range(world) if r in out and "error" in out[r]}
+    assert not errors, "\n".join(f"rank {r}:\n{e}" for r, e in errors.items())
+    assert not hung, "a rank hung"
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     for rank in range(world):
         res = out[rank]
