@@ -16,27 +16,35 @@
 //     dQ_i partial = dS K_r                 A = the same dS^T tile read MN-major (i.e. transposed),
 //                                           B = K_r read MN-major; rows = queries
 //   dQ_i is the sum of the two CTAs' partials.  The partial for the PARTNER's query tile is computed
-//   first and written, as fp32, into the partner's shared memory (distributed shared memory); the
-//   partial for the CTA's own tile is computed second, the partner's contribution is added to it in a
-//   fixed order (own + partner), and the owner scales, rounds and stores dQ_i.  No atomics, no
-//   workspace, bit-reproducible.
+//   first, staged as fp32 in local shared memory and moved into the partner's shared memory by ONE
+//   bulk asynchronous copy (cp.async.bulk shared::cta -> shared::cluster, completion counted on the
+//   partner's barrier; thread-issued remote stores of the same 40 KB took 7600 cycles).  It lands in
+//   the partner's slot of the step-0 tiles, which are dead by then (both CTAs' step-0 products commit
+//   to one barrier of each CTA with a multicast tcgen05.commit, so "the partner's slot is dead" costs
+//   no software handshake).  The receiver moves the partial from shared memory into the S columns of
+//   its tensor memory, and its own partial, computed second, is ACCUMULATED onto it by the tensor
+//   core (partner + own, a fixed order); the owner then scales, rounds and stores dQ_i.  No atomics,
+//   no workspace, bit-reproducible.
 //
-//   delta_i = rowsum(dO_i * O_i) and -lse_i log2 e are produced per query tile by the P warps from
-//   shared-memory tiles (the forward output O_i is loaded for that alone).
+//   -lse_i log2 e is formed by the P warps from the lse row that travels with the tiles; delta_i =
+//   rowsum(dO_i * O_i) by the D warps from shared-memory tiles while the P warps turn S into P (the
+//   forward output O_i is loaded for that alone).
 //
-// The partial dQ of the first step lands in the S columns (free once the second S has been read), that
-// of the second step in the dP columns (free once the second dP has been read): tensor memory is
+// Both dQ partials use the S columns (free once the second S has been read): the one for the partner is
+// drained from there, the partner's is written there, the own one is accumulated there.  Tensor memory:
 // S 128 | dP 128 | P 64 | dK DPAD | dV DPAD = 480 columns at head_dim 72.
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 P warps (vectors, S -> P,
-// the dQ partials: exchange, sum, store), warps 6-9 D warps (dP, P -> dS; dK / dV epilogue).
+// Warp roles (352 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 P warps (S -> P; the dQ
+// partials: exchange, final tile), warps 6-9 D warps (delta; dP, P -> dS; dK / dV tiles), warp 10 issues
+// the TMA stores of the three staged output tiles (an issuing thread stalls for a thousand cycles and more
+// when the TMA queue is full of the next head's loads; in a warp of its own that stalls nobody else).
 #pragma once
 
 #include "attn_bwd.cuh"
 
 namespace dmf {
 
-constexpr int kBwdFusedThreads = 320;
+constexpr int kBwdFusedThreads = 352;  // TMA warp, MMA warp, four P warps, four D warps, store warp
 constexpr int kBwdFusedSeqlen = 256;  // the only sequence length this kernel takes (two tiles)
 
 struct BwdFusedParams {
@@ -61,9 +69,10 @@ struct BwdFusedTraits {
   static constexpr int kGroupBytes = 2 * kTileBytes;  // (K, V) or (Q_i, dO_i)
   static constexpr int kStages = 2;                   // one per step of a head
   static constexpr int kDsBytes = 128 * 128 * 2;      // dS^T: two atoms of 64 query columns, 128-byte rows
-  static constexpr int kXchgBytes = 128 * kDPad * 4;  // fp32 dQ partial from the partner: [column / 4][row][4]
+  static constexpr int kXchgBytes = 128 * kDPad * 4;  // an fp32 dQ partial: [column / 4][row][4]
   static constexpr int kVecBytes = 2 * 128 * 4;       // per step: -lse*log2e[128], delta[128]
-  static_assert(kTileBytes <= kDsBytes && kTileBytes <= kXchgBytes, "output staging aliases these buffers");
+  static_assert(kTileBytes <= kDsBytes && 2 * kTileBytes <= kXchgBytes, "output staging aliases these buffers");
+  static_assert(kXchgBytes <= kGroupBytes, "the partner's partial is received in the slot of the step-0 tiles");
   // offsets from the 1024-byte aligned base
   static constexpr int kOffKV = 0;
   static constexpr int kOffX = kOffKV + kGroupBytes;
@@ -75,8 +84,9 @@ struct BwdFusedTraits {
   static constexpr int kOffBars = kOffVec + kStages * kVecBytes;
   static constexpr int kBarKVFull = 0, kBarXFull = 1 /* +stage */, kBarXEmpty = 3 /* +stage */, kBarOFull = 5,
                        kBarOEmpty = 6, kBarSFull = 7, kBarSEmpty = 8, kBarDFull = 9, kBarPFull = 10, kBarPEmpty = 11,
-                       kBarGFull = 12, kBarVecFull = 13 /* +stage */, kBarDpFree = 15, kBarAccEmpty = 16,
-                       kBarXchgFull = 17, kBarXchgEmpty = 18, kNumBars = 19;
+                       kBarGFull = 12, kBarRecvInTmem = 15, kBarAccEmpty = 16,
+                       kBarXchgFull = 17, kBarX0Both = 18, kBarSendDone = 19, kBarX0Free = 20, kBarQStaged = 21,
+                       kBarKVStaged = 22, kBarStageFree = 13, kNumBars = 23;
   static constexpr int kSmemBytes = 1024 + kOffBars + kNumBars * 8 + 16;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
   static constexpr uint32_t kColS = 0, kColD = 128, kColP = 256, kColDK = 320, kColDV = 320 + kDPad;
@@ -86,38 +96,31 @@ struct BwdFusedTraits {
   static constexpr uint32_t kTailRowBytes = 2 * TAIL;
 };
 
-// ---- cluster-scope helpers used only here ----
+// ---- cluster helpers used only here ----
 
-// arrive on a barrier of the other CTA, publishing this thread's earlier writes to its shared memory
-__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+// Arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair once every tcgen05 operation issued
+// so far by this thread (a cta_group::1 issuer) has completed.
+__device__ __forceinline__ void tc_commit_both(uint32_t bar, bool issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      ".reg .b16 m;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "mov.b16 m, 3;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t"
+      "}"
+      ::"r"(bar), "r"(static_cast<uint32_t>(issue))
+      : "memory");
 }
-__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
-__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d)
+
+// Bulk asynchronous copy of `bytes` (a multiple of 16) from this CTA's shared memory into another CTA's; the
+// transaction bytes are counted on a barrier of the destination CTA.  Both destination operands are
+// shared::cluster addresses (mapa).  Not a multicast copy, and not a load from global memory.
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t src_smem, uint32_t bytes,
+                                                 uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster), "r"(src_smem), "r"(bytes), "r"(bar_cluster)
                : "memory");
-}
-
-// Bounded wait with cluster-scope acquire: for a barrier the OTHER CTA arrives on after writing this
-// CTA's shared memory.  Same limit, abort flag and status code conventions as mbar_wait.
-__device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                               int32_t* status_word, int32_t code) {
-  uint32_t spins = 0;
-  long long t0 = 0;
-  while (true) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((++spins & 255u) == 0u) {
-      if (*abort_flag != 0) return false;
-      const long long now = clock64();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > kWaitLimitCycles) {
-        *abort_flag = 1;
-        if (status_word != nullptr) atomicCAS(status_word, 0, code);
-        return false;
-      }
-    }
-  }
 }
 
 // acc[128 x (64 + TAIL)] (+)= A[128 x 128] * B[128 x (64 + TAIL)], A 16-bit in SHARED memory as two atoms of
@@ -144,7 +147,8 @@ __device__ __forceinline__ void issue_smem_a_pv(bool leader, uint32_t d_tmem, ui
   }
 }
 
-constexpr int kRoleXchg = 400;  // status codes of the waits on the partner CTA
+
+constexpr int kRoleStore = 500;  // status codes of the store warp's waits (role * 100 + barrier, like the others)
 
 // In-kernel timeline, compiled in only with -DDMF_TRACE (diagnostic builds): the first thread of each role in
 // cluster 0 appends (SM cycle counter << 8 | event id) to a per-CTA, per-role list in device memory, which a
@@ -177,7 +181,8 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
   const uint32_t s_kv = s_base + TR::kOffKV, s_x = s_base + TR::kOffX, s_o = s_base + TR::kOffO;
   const uint32_t s_ds = s_base + TR::kOffDs, s_xchg = s_base + TR::kOffXchg, s_lse = s_base + TR::kOffLse;
   uint8_t* ds_tile = smem + TR::kOffDs;      // dS^T of the current step; between heads: staging of dK, dV
-  uint8_t* xchg = smem + TR::kOffXchg;       // the partner's dQ partial; afterwards: staging of dQ
+  uint8_t* send = smem + TR::kOffXchg;       // this CTA's dQ partial for the partner; at the end of a head: staging of dQ, dV
+  const uint8_t* recv = smem + TR::kOffX;    // the partner's dQ partial for this CTA, in the slot of the step-0 tiles
   const float* lse_raw = reinterpret_cast<const float*>(smem + TR::kOffLse);   // [stage][128]
   float* vec = reinterpret_cast<float*>(smem + TR::kOffVec);                   // [stage][2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TR::kOffBars);
@@ -199,10 +204,11 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
     for (int i = 0; i < TR::kNumBars; ++i) {
       uint32_t count = 1;  // TMA transaction or tcgen05.commit
       if (i == TR::kBarOEmpty || i == TR::kBarSEmpty || i == TR::kBarPFull || i == TR::kBarGFull ||
-          i == TR::kBarVecFull || i == TR::kBarVecFull + 1 || i == TR::kBarDpFree || i == TR::kBarAccEmpty ||
-          i == TR::kBarXchgFull)
+          i == TR::kBarRecvInTmem || i == TR::kBarAccEmpty || i == TR::kBarX0Free || i == TR::kBarQStaged ||
+          i == TR::kBarKVStaged)
         count = 4;                                  // one arrival per warp of a group
       if (i == TR::kBarPEmpty) count = 5;           // the commit behind dV += P^T dO, and the four D warps
+      if (i == TR::kBarX0Both) count = 2;           // the step-0 commits of both CTAs (multicast)
       mbar_init(bar(i), count);
     }
     fence_mbar_init();
@@ -238,9 +244,10 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
 #pragma unroll 1
         for (int step = 0; ok && step < 2; ++step) {
           const int q0 = q_tile_of(step) * 128;
-          // (Q_i, dO_i) and the lse row of the tile: the slot was freed by the last product of the same step
-          // of the previous head
-          ok = wait(TR::kBarXEmpty + step, ph ^ 1u);
+          // (Q_i, dO_i) and the lse row of the tile.  Slot 1 is freed by the last product of the previous head;
+          // slot 0 receives the partner's dQ partial in the second half of a head and is free once the P warps
+          // have read that
+          ok = wait(step == 0 ? TR::kBarX0Free : TR::kBarXEmpty + 1, ph ^ 1u);
           if (!ok) break;
           {
             const uint32_t dst = s_x + step * TR::kGroupBytes, fb = bar(TR::kBarXFull + step);
@@ -318,11 +325,7 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
       issue_qk<TAIL, TR>(leader, t_s, k_tile, q0_tile, idesc_qk, false);     // S_0^T = K Q_0^T
       commit(TR::kBarSFull);
       DMF_TRACE_EVENT(1, 11);
-      if (hcnt > 0) {  // the previous head's second dQ partial (in the dP columns) has been read
-        ok = wait(TR::kBarDpFree, (hcnt - 1u) & 1u);
-        if (!ok) break;
-        tc_fence_after_sync();
-      }
+      // (the dP columns are free: the D warps had read dP_1 of the previous head before its last products were issued)
       issue_qk<TAIL, TR>(leader, t_d, v_tile, do0_tile, idesc_qk, false);    // dP_0^T = V dO_0^T
       commit(TR::kBarDFull);
       DMF_TRACE_EVENT(1, 12);
@@ -347,7 +350,8 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
       DMF_TRACE_EVENT(1, 16);
       issue_smem_a_pv<TAIL, TR, false>(leader, t_dk, s_ds, q0_tile, idesc_pv_main, idesc_pv_tail, false);
       issue_smem_a_pv<TAIL, TR, true>(leader, t_s, s_ds, k_tile, idesc_tr_main, idesc_tr_tail, false);
-      commit(TR::kBarXEmpty + 0);  // slot 0 free; dS buffer free; the first dQ partial is complete
+      commit(TR::kBarXEmpty + 0);  // dS buffer free; the first dQ partial is complete
+      tc_commit_both(bar(TR::kBarX0Both), leader);  // ... in both CTAs: each CTA's slot 0 can receive the other's partial
       // ---- step 1 ----
       issue_qk<TAIL, TR>(leader, t_d, v_tile, do1_tile, idesc_qk, false);    // dP_1^T (dP_0 was read before dS_0 was signalled)
       commit(TR::kBarDFull);
@@ -363,9 +367,41 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
       tc_fence_after_sync();
       DMF_TRACE_EVENT(1, 19);
       issue_smem_a_pv<TAIL, TR, false>(leader, t_dk, s_ds, q1_tile, idesc_pv_main, idesc_pv_tail, true);
-      issue_smem_a_pv<TAIL, TR, true>(leader, t_d, s_ds, k_tile, idesc_tr_main, idesc_tr_tail, false);
+      ok = wait(TR::kBarRecvInTmem, ph);            // the partner's partial of this CTA's dQ tile sits in the S columns
+      if (!ok) break;
+      tc_fence_after_sync();
+      issue_smem_a_pv<TAIL, TR, true>(leader, t_s, s_ds, k_tile, idesc_tr_main, idesc_tr_tail, true);  // += dS_1 K
       commit(TR::kBarXEmpty + 1);  // slot 1, K/V and the dS buffer free; dK, dV and the second dQ partial complete
       DMF_TRACE_EVENT(1, 20);
+    }
+  } else if (warp == 10) {
+    // ============================== store warp ==============================
+    if (lane == 0) {
+      uint32_t hcnt = 0;
+      bool ok = true;
+      auto wait = [&](int b_, uint32_t parity) -> bool {
+        return mbar_wait(bar(b_), parity, abort_flag, p.status_word, kRoleStore + b_);
+      };
+      for (int bh = cluster_id; ok && bh < p.num_heads_total; bh += num_clusters, ++hcnt) {
+        const int b = bh / p.heads, h = bh % p.heads;
+        const uint32_t ph = hcnt & 1u;
+        const int r0 = static_cast<int>(rank) * 128;   // this CTA's query tile and key tile
+        ok = wait(TR::kBarQStaged, ph);
+        if (!ok) break;
+        tma_store_4d(&p.dq_main, s_xchg, 0, r0, h, b);
+        if constexpr (TAIL > 0) tma_store_4d(&p.dq_tail, s_xchg + TR::kMainBytes, 64, r0, h, b);
+        tma_store_commit();
+        ok = wait(TR::kBarKVStaged, ph);
+        if (!ok) break;
+        tma_store_4d(&p.dk_main, s_ds, 0, r0, h, b);
+        if constexpr (TAIL > 0) tma_store_4d(&p.dk_tail, s_ds + TR::kMainBytes, 64, r0, h, b);
+        tma_store_4d(&p.dv_main, s_xchg + TR::kTileBytes, 0, r0, h, b);
+        if constexpr (TAIL > 0) tma_store_4d(&p.dv_tail, s_xchg + TR::kTileBytes + TR::kMainBytes, 64, r0, h, b);
+        tma_store_commit();
+        tma_store_wait_read();                 // all three staging tiles have been read
+        mbar_arrive(bar(TR::kBarStageFree));
+      }
+      tma_store_wait_all();
     }
   } else {
     // ====================== P warps and D warps =============================
@@ -389,7 +425,7 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
       return static_cast<uint32_t>(TR::kMainBytes + row * 32 + ((ct ^ ((row >> 2) & 1)) << 4));
     };
     const int bar_id = p_role ? 2 : 1;  // hardware barrier of the role's 128 threads
-    const bool mover = (lane == 0) && (warp == (p_role ? 2 : 6));  // issues the role's TMA stores
+    const bool mover = (lane == 0) && (warp == 2);  // the P warps' thread for one-per-CTA actions
 
     // Failure handling: a wait that gives up makes `ok` false.  From then on a warp skips all work but still walks
     // through every hardware-barrier meeting of the head (they AND everybody's `ok`, so the whole role agrees),
@@ -403,33 +439,11 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
         for (int step = 0; step < 2; ++step) {
           const uint32_t g = 2u * hcnt + static_cast<uint32_t>(step);
           float* vstage = vec + step * 256;
-          // ---- the step's vectors: -lse * log2e and delta = rowsum(dO * O), one query row per thread ----
+          // ---- -lse * log2e of the step's 128 queries (the lse row arrives with the step's tiles) ----
           if (ok) ok = wait(TR::kBarXFull + step, ph);
-          if (ok) ok = wait(TR::kBarOFull, g & 1u);
           if (warp == 2) DMF_TRACE_EVENT(2, 30);
-          if (ok) {
-            const uint8_t* do_tile = smem + TR::kOffX + step * TR::kGroupBytes + TR::kTileBytes;
-            const uint8_t* o_tile = smem + TR::kOffO;
-            float acc = 0.f;
-#pragma unroll
-            for (int c = 0; c < DPAD / 8; ++c) {
-              const uint32_t off = chunk_off(c * 8);
-              const uint4 ov = *reinterpret_cast<const uint4*>(o_tile + off);
-              const uint4 dv = *reinterpret_cast<const uint4*>(do_tile + off);
-              const uint32_t ou[4] = {ov.x, ov.y, ov.z, ov.w}, du[4] = {dv.x, dv.y, dv.z, dv.w};
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 a = unpack2<T>(ou[i]), g2 = unpack2<T>(du[i]);
-                acc = fmaf(a.x, g2.x, acc);
-                acc = fmaf(a.y, g2.y, acc);
-              }
-            }
-            vstage[row] = -lse_raw[step * 128 + row] * 1.4426950408889634f;
-            vstage[128 + row] = acc;
-            mbar_arrive_warp(bar(TR::kBarOEmpty));          // o has been read
-            mbar_arrive_warp(bar(TR::kBarVecFull + step));  // for the D warps (the arrive releases the writes above)
-          }
-          ok = named_bar_and(bar_id, 128, ok);  // the vectors of all 128 rows are visible to the P warps
+          if (ok) vstage[row] = -lse_raw[step * 128 + row] * 1.4426950408889634f;
+          ok = named_bar_and(bar_id, 128, ok);  // all 128 values are visible to the P warps
           if (warp == 2) DMF_TRACE_EVENT(2, 31);
           // ---- P^T = exp2(S^T * c - lse2), 16-bit, into the P columns ----
           if (ok) ok = wait(TR::kBarSFull, g & 1u);
@@ -474,17 +488,16 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
             }
           }
         }
-        // ---- the partner's dQ partial (step 0, in the S columns): fp32 into the partner's exchange buffer ----
-        if (ok) ok = wait(TR::kBarXEmpty + 0, ph);
-        if (ok && hcnt > 0) {
-          // the partner has finished with what this CTA wrote for the previous head
-          ok = __all_sync(0xffffffffu, mbar_wait_cluster(bar(TR::kBarXchgEmpty), (hcnt - 1u) & 1u, abort_flag,
-                                                         p.status_word, kRoleXchg + TR::kBarXchgEmpty));
-        }
+        // ---- the partner's dQ partial (step 0, in the S columns): staged as fp32, one bulk copy to the partner ----
+        // both CTAs' step-0 products are complete: the partial is there, and the step-0 tiles of BOTH CTAs are dead
+        if (ok) ok = wait(TR::kBarX0Both, ph);
+        // the completion of the partner's copy into this CTA's slot 0 is counted here
+        if (ok && mover) mbar_arrive_expect_tx(bar(TR::kBarXchgFull), TR::kXchgBytes);
+        // the stores of the previous head's dQ and dV tiles have read the region the partial is staged in
+        if (ok && hcnt > 0) ok = wait(TR::kBarStageFree, (hcnt - 1u) & 1u);
         if (ok) {
           tc_fence_after_sync();
           if (warp == 2) DMF_TRACE_EVENT(2, 35);
-          const uint32_t remote = map_to_cta(s_xchg, peer);
 #pragma unroll
           for (int c = 0; c < DPAD / 16; ++c) {
             uint32_t a[16];
@@ -492,79 +505,111 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              st_shared_cluster_v4(remote + static_cast<uint32_t>(((c * 4 + i) * 128 + row) * 16), __uint_as_float(a[4 * i]),
-                                   __uint_as_float(a[4 * i + 1]), __uint_as_float(a[4 * i + 2]), __uint_as_float(a[4 * i + 3]));
+              *reinterpret_cast<uint4*>(send + ((c * 4 + i) * 128 + row) * 16) = make_uint4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
           }
-          tc_fence_before_sync();
-          mbar_arrive_warp(bar(TR::kBarSEmpty));  // the S columns are free for the next head
-          if (lane == 0) {                        // (the arrive above synchronised the warp)
-            fence_acq_rel_cluster();
-            mbar_arrive_release_cluster(map_to_cta(bar(TR::kBarXchgFull), peer));
-          }
-          if (warp == 2) DMF_TRACE_EVENT(2, 36);
+          fence_proxy_async_smem();
         }
-        // ---- this CTA's own dQ tile: own partial (step 1, in the dP columns) + the partner's, scaled, stored ----
-        if (ok) ok = wait(TR::kBarXEmpty + 1, ph);
+        ok = named_bar_and(bar_id, 128, ok);         // all 128 rows are staged
+        if (ok && mover) {
+          bulk_copy_to_cta(map_to_cta(s_x, peer), s_xchg, TR::kXchgBytes, map_to_cta(bar(TR::kBarXchgFull), peer));
+          DMF_TRACE_EVENT(2, 36);
+        }
+        // ---- the partner's partial of this CTA's own dQ tile: shared memory -> the S columns ----
         if (ok)
-          ok = __all_sync(0xffffffffu, mbar_wait_cluster(bar(TR::kBarXchgFull), ph, abort_flag, p.status_word,
-                                                         kRoleXchg + TR::kBarXchgFull));
-        uint32_t packed[DPAD / 2];
+          ok = wait(TR::kBarXchgFull, ph);             // (transaction bytes of an asynchronous copy, like a TMA load)
         if (ok) {
-          tc_fence_after_sync();
           if (warp == 2) DMF_TRACE_EVENT(2, 37);
 #pragma unroll
           for (int c = 0; c < DPAD / 16; ++c) {
             uint32_t a[16];
-            tmem_ld_x16(t_d + c * 16, a);
-            tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const float4 o4 = *reinterpret_cast<const float4*>(xchg + ((c * 4 + i) * 128 + row) * 16);
-              const float x0 = (__uint_as_float(a[4 * i]) + o4.x) * p.scale;
-              const float x1 = (__uint_as_float(a[4 * i + 1]) + o4.y) * p.scale;
-              const float x2 = (__uint_as_float(a[4 * i + 2]) + o4.z) * p.scale;
-              const float x3 = (__uint_as_float(a[4 * i + 3]) + o4.w) * p.scale;
-              packed[c * 8 + 2 * i] = Pack2<T>::pack(x0, x1);
-              packed[c * 8 + 2 * i + 1] = Pack2<T>::pack(x2, x3);
+              const uint4 o4 = *reinterpret_cast<const uint4*>(recv + ((c * 4 + i) * 128 + row) * 16);
+              a[4 * i] = o4.x; a[4 * i + 1] = o4.y; a[4 * i + 2] = o4.z; a[4 * i + 3] = o4.w;
+            }
+            tmem_st_x16(t_s + c * 16, a);
+          }
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive_warp(bar(TR::kBarRecvInTmem)); // the own partial can be accumulated onto it
+          mbar_arrive_warp(bar(TR::kBarX0Free));     // slot 0 is free for the next head's step-0 tiles
+          // tell the partner that its copy has arrived (its staging region is free again).  Nothing this thread
+          // wrote is read by the partner on the strength of this arrival, so it carries no cluster-scope release
+          // (such a release costs thousands of cycles here)
+          if (warp == 5 && lane == 0) mbar_arrive_cluster(map_to_cta(bar(TR::kBarSendDone), peer));
+          if (warp == 2) DMF_TRACE_EVENT(2, 40);
+        }
+        // ---- this CTA's own dQ tile: partner's partial + own (accumulated by the tensor core), scaled, stored ----
+        if (ok) ok = wait(TR::kBarXEmpty + 1, ph);
+        uint32_t packed[DPAD / 2];
+        if (ok) {
+          tc_fence_after_sync();
+          if (warp == 2) DMF_TRACE_EVENT(2, 41);
+          const uint64_t scale2 = pack_f2(p.scale, p.scale);
+#pragma unroll
+          for (int c = 0; c < DPAD / 16; ++c) {
+            uint32_t a[16];
+            tmem_ld_x16(t_s + c * 16, a);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float x0, x1;
+              unpack_f2(mul2(pack_u2(a[2 * i], a[2 * i + 1]), scale2), x0, x1);
+              packed[c * 8 + i] = Pack2<T>::pack(x0, x1);
             }
           }
           tc_fence_before_sync();
-          mbar_arrive_warp(bar(TR::kBarDpFree));  // the dP columns are free for the next head
+          mbar_arrive_warp(bar(TR::kBarSEmpty));     // the S columns are free for the next head
+          // this CTA's own copy has arrived at the partner (signalled long ago): the staging region can take the dQ tile
+          ok = wait(TR::kBarSendDone, ph);
         }
-        ok = named_bar_and(bar_id, 128, ok);  // everybody has read the exchange buffer: it becomes the staging tile
         if (ok) {
 #pragma unroll
           for (int c = 0; c < DPAD / 8; ++c)
-            *reinterpret_cast<uint4*>(xchg + chunk_off(c * 8)) =
+            *reinterpret_cast<uint4*>(send + chunk_off(c * 8)) =
                 make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
           fence_proxy_async_smem();
+          mbar_arrive_warp(bar(TR::kBarQStaged));    // for the store warp
         }
-        ok = named_bar_and(bar_id, 128, ok);  // dQ is staged
         if (warp == 2) DMF_TRACE_EVENT(2, 38);
-        if (ok && mover) {
-          const int q0 = static_cast<int>(rank) * 128;
-          tma_store_4d(&p.dq_main, s_xchg, 0, q0, h, b);
-          if constexpr (TAIL > 0) tma_store_4d(&p.dq_tail, s_xchg + TR::kMainBytes, 64, q0, h, b);
-          tma_store_commit();
-          tma_store_wait_read();  // the partner may write the buffer again
-          fence_acq_rel_cluster();
-          mbar_arrive_release_cluster(map_to_cta(bar(TR::kBarXchgEmpty), peer));
-          DMF_TRACE_EVENT(2, 39);
-        }
       } else {
         // ================================ D warps ================================
 #pragma unroll 1
         for (int step = 0; step < 2; ++step) {
           const uint32_t g = 2u * hcnt + static_cast<uint32_t>(step);
-          const float* vstage = vec + step * 256;
-          if (ok) ok = wait(TR::kBarVecFull + step, ph);
+          float* vstage = vec + step * 256;
+          // ---- delta = rowsum(dO * O) of the step's 128 queries, one query row per thread, from the shared-memory
+          // tiles (this role would otherwise sit idle until the first P of the step exists) ----
+          if (ok) ok = wait(TR::kBarXFull + step, ph);
+          if (ok) ok = wait(TR::kBarOFull, g & 1u);
+          if (ok) {
+            const uint8_t* do_tile = smem + TR::kOffX + step * TR::kGroupBytes + TR::kTileBytes;
+            const uint8_t* o_tile = smem + TR::kOffO;
+            float acc = 0.f;
+#pragma unroll
+            for (int c = 0; c < DPAD / 8; ++c) {
+              const uint32_t off = chunk_off(c * 8);
+              const uint4 ov = *reinterpret_cast<const uint4*>(o_tile + off);
+              const uint4 dv = *reinterpret_cast<const uint4*>(do_tile + off);
+              const uint32_t ou[4] = {ov.x, ov.y, ov.z, ov.w}, du[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 a = unpack2<T>(ou[i]), g2 = unpack2<T>(du[i]);
+                acc = fmaf(a.x, g2.x, acc);
+                acc = fmaf(a.y, g2.y, acc);
+              }
+            }
+            vstage[128 + row] = acc;
+            mbar_arrive_warp(bar(TR::kBarOEmpty));  // o has been read
+          }
+          if (warp == 6) DMF_TRACE_EVENT(3, 56);
           if (ok) ok = wait(TR::kBarPFull, g & 1u);
           if (ok) ok = wait(TR::kBarDFull, g & 1u);
-          // the dS buffer: free when the products of the step before (this head's step 0, or the previous head's
-          // step 1 followed by its dK / dV stores, which this role issued itself) are done with it
+          // the dS buffer: free when the products of the step before (this head's step 0) are done with it, or the
+          // store of the previous head's dK tile, which was staged there
           if (ok && step == 1) ok = wait(TR::kBarXEmpty + 0, ph);
-          if (step == 0 && hcnt > 0 && mover) tma_store_wait_read();
-          ok = named_bar_and(bar_id, 128, ok);
+          if (ok && step == 0 && hcnt > 0) ok = wait(TR::kBarStageFree, (hcnt - 1u) & 1u);
+          ok = named_bar_and(bar_id, 128, ok);       // (delta of all 128 queries is visible to the D warps)
           if (warp == 6) DMF_TRACE_EVENT(3, 50);
           if (ok) {
             tc_fence_after_sync();
@@ -600,13 +645,16 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
             if (warp == 6) DMF_TRACE_EVENT(3, 51);
           }
         }
-        // ---- epilogue: dK (scaled) and dV through the staging tile (the dS buffer) ----
+        // ---- epilogue: dK (scaled) staged in the dS buffer, dV in the second half of the send region ----
         if (ok) ok = wait(TR::kBarXEmpty + 1, ph);  // every product of the head is complete
+        // the send region: this CTA's copy to the partner has arrived there
+        if (ok)
+          ok = wait(TR::kBarSendDone, ph);
         ok = named_bar_and(bar_id, 128, ok);
         if (warp == 6) DMF_TRACE_EVENT(3, 52);
-        uint32_t p1[DPAD / 2];
         if (ok) {
           tc_fence_after_sync();
+          uint8_t* dv_stage = send + TR::kTileBytes;
           const uint64_t scale2 = pack_f2(p.scale, p.scale);
 #pragma unroll
           for (int c = 0; c < DPAD / 16; ++c) {
@@ -614,51 +662,29 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
             tmem_ld_x16(t_dk + c * 16, a);
             tmem_ld_x16(t_dk + DPAD + c * 16, v);
             tmem_wait_ld();
-            uint32_t p0[8];
+            uint32_t p0[8], p1[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               float x0, x1;
               unpack_f2(mul2(pack_u2(a[2 * i], a[2 * i + 1]), scale2), x0, x1);
               p0[i] = Pack2<T>::pack(x0, x1);
-              p1[c * 8 + i] = Pack2<T>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+              p1[i] = Pack2<T>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
             }
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh)
-              *reinterpret_cast<uint4*>(ds_tile + chunk_off(c * 16 + hh * 8)) =
-                  make_uint4(p0[4 * hh], p0[4 * hh + 1], p0[4 * hh + 2], p0[4 * hh + 3]);
+            for (int hh = 0; hh < 2; ++hh) {
+              const uint32_t off = chunk_off(c * 16 + hh * 8);
+              *reinterpret_cast<uint4*>(ds_tile + off) = make_uint4(p0[4 * hh], p0[4 * hh + 1], p0[4 * hh + 2], p0[4 * hh + 3]);
+              *reinterpret_cast<uint4*>(dv_stage + off) = make_uint4(p1[4 * hh], p1[4 * hh + 1], p1[4 * hh + 2], p1[4 * hh + 3]);
+            }
           }
           tc_fence_before_sync();
           mbar_arrive_warp(bar(TR::kBarAccEmpty));  // the next head may overwrite dK, dV
           fence_proxy_async_smem();
+          mbar_arrive_warp(bar(TR::kBarKVStaged));  // for the store warp
         }
-        ok = named_bar_and(bar_id, 128, ok);  // dK is staged
         if (warp == 6) DMF_TRACE_EVENT(3, 53);
-        const int k0 = static_cast<int>(rank) * 128;
-        if (ok && mover) {
-          tma_store_4d(&p.dk_main, s_ds, 0, k0, h, b);
-          if constexpr (TAIL > 0) tma_store_4d(&p.dk_tail, s_ds + TR::kMainBytes, 64, k0, h, b);
-          tma_store_commit();
-          tma_store_wait_read();
-        }
-        ok = named_bar_and(bar_id, 128, ok);  // the store of dK has read the tile
-        if (warp == 6) DMF_TRACE_EVENT(3, 54);
-        if (ok) {
-#pragma unroll
-          for (int c = 0; c < DPAD / 8; ++c)
-            *reinterpret_cast<uint4*>(ds_tile + chunk_off(c * 8)) =
-                make_uint4(p1[4 * c], p1[4 * c + 1], p1[4 * c + 2], p1[4 * c + 3]);
-          fence_proxy_async_smem();
-        }
-        ok = named_bar_and(bar_id, 128, ok);  // dV is staged
-        if (warp == 6) DMF_TRACE_EVENT(3, 55);
-        if (ok && mover) {
-          tma_store_4d(&p.dv_main, s_ds, 0, k0, h, b);
-          if constexpr (TAIL > 0) tma_store_4d(&p.dv_tail, s_ds + TR::kMainBytes, 64, k0, h, b);
-          tma_store_commit();
-        }
       }
     }
-    if (mover) tma_store_wait_all();
   }
 
   // ============================== teardown ==================================
