@@ -44,14 +44,18 @@ def _worker(rank, world, port, out):
             x_t, v = (1 - t) * x + t * eps, eps - x
             # flow-matching term through `model` (the DDP wrapper in the eager mode: its forward is what arms the
             # gradient reducer), MeanFlow term through the raw module under torch.func.jvp, as DMFLoss does
-            v_fm, _ = model(x_t, t, t, y, return_logvar=True)
-            (u, _), (du, _) = torch.func.jvp(partial(raw, y=y, return_logvar=True), (x_t, t, r),
-                                             (v, torch.ones_like(t), torch.zeros_like(r)))
+            v_fm, lv_fm = model(x_t, t, t, y, return_logvar=True)
+            (u, lv_mf), (du, _) = torch.func.jvp(partial(raw, y=y, return_logvar=True), (x_t, t, r),
+                                                 (v, torch.ones_like(t), torch.zeros_like(r)))
             fm = ((v_fm - v) ** 2).mean(dim=(1, 2, 3))
-            return 0.5 * (fm + ((u - (v + (r - t) * du).detach()) ** 2).mean(dim=(1, 2, 3))), {}
+            mf = ((u - (v + (r - t) * du).detach()) ** 2).mean(dim=(1, 2, 3))
+            # the log-variance heads take part too (every parameter receives a gradient, as DDP expects)
+            return 0.5 * (fm / lv_fm.flatten().exp() + lv_fm.flatten() + mf / lv_mf.flatten().exp() + lv_mf.flatten()), {}
 
         grads, losses = {}, {}
+        say = lambda *a: print(f"[rank {rank}]", *a, flush=True)
         for mode in ("overlap", "single", "ddp"):
+            say("mode", mode)
             st = T.build_train_state(dev, name="DMFT-S/2", input_size=32, dmf_depth=8, attn_func="fa3", seed=0,
                                      zero_init=False, graphs=(mode != "ddp"), overlap=(mode == "overlap"), n_buckets=4)
             st.loss_fn = fixed_loss
@@ -59,7 +63,8 @@ def _worker(rank, world, port, out):
             batches = [T.synthetic_batch(st, 4, generator=bgen) for _ in range(2)]
             if mode == "ddp":
                 loss = T.accumulate_eager(st, batches)
-                flat = torch.cat([p.grad.flatten() for p in st.model.parameters() if p.requires_grad])
+                flat = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).flatten()
+                                  for p in st.model.parameters() if p.requires_grad])
             else:
                 loss = T.accumulate_graphed(st, batches)
                 flat = st.flat_grad.clone()
@@ -74,6 +79,7 @@ def _worker(rank, world, port, out):
         res = {"overlap_vs_ddp": rel(grads["overlap"], grads["ddp"]), "single_vs_ddp": rel(grads["single"], grads["ddp"]),
                "loss_overlap": losses["overlap"], "loss_ddp": losses["ddp"],
                "grad_norm": float(grads["ddp"].norm())}
+        say("gradients compared", res)
         # one whole optimisation step with the real loss on the overlapped path: parameters stay identical across ranks
         st = T.build_train_state(dev, name="DMFT-S/2", input_size=32, dmf_depth=8, attn_func="fa3", seed=0,
                                  zero_init=False, graphs=True, overlap=True, n_buckets=4)
@@ -89,12 +95,22 @@ def _worker(rank, world, port, out):
         res["loss_finite"] = bool(torch.isfinite(loss))
         ops.check_device_status(dev)
         out[rank] = res
+        say("done")
     except BaseException:
         # report, and leave without tearing the process group down: after a failure in the middle of a sequence of
         # collectives the teardown itself can block on the other rank
         out[rank] = {"error": traceback.format_exc()}
         os._exit(1)
+    # Graphs that hold captured collectives must be gone before the communicator is (the teardown otherwise waits for
+    # them for ever); and if the teardown still does not return, leave anyway: the results are already with the parent.
+    import gc
+    import threading
+    del st
+    gc.collect()
+    torch.cuda.synchronize(dev)
+    threading.Timer(20.0, lambda: os._exit(0)).start()
     dist.destroy_process_group()
+    os._exit(0)
 
 
 def test_graphed_allreduce_matches_ddp_on_two_gpus():
