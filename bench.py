@@ -1066,7 +1066,7 @@ def _model_record(args, workload, world, rank, dev, steps=None, warm=None):
     return rec
 
 
-def _model_record_in_children(args, workload, world, rank, local_rank, port_offset, limit_s=420):
+def _model_record_in_children(args, workload, world, rank, local_rank, port_offset, limit_s=300):
     """A whole-model configuration for the default line, run as a job of its own: every rank of this job starts one
     child process (`bench.py --workload C4|C5 --record-only`), the children form their own process group on another
     port, and rank 0's child prints the record.  A failure or a stall in there costs the sub-record (the child is
@@ -1117,8 +1117,8 @@ def run_model(args):
     _pin_to_gpu_numa_node(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # a collective that cannot complete ends the job with an error after three minutes instead of blocking it
-        dist.init_process_group("nccl", device_id=dev, timeout=__import__("datetime").timedelta(seconds=180))
+        # a collective that cannot complete ends the job with an error after two minutes instead of blocking it
+        dist.init_process_group("nccl", device_id=dev, timeout=__import__("datetime").timedelta(seconds=120))
     rec = _model_record(args, args.workload, world, rank, dev,
                         steps=None if args.steps == 50 else args.steps, warm=None if args.warmup == 10 else args.warmup)
     if rank == 0 and args.record_only:

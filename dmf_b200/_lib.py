@@ -30,6 +30,7 @@ EXPORTS = (
     "dmf_rmsnorm_fwd", "dmf_rmsnorm_bwd", "dmf_rmsnorm_bwd_workspace_bytes",
     "dmf_ln_modulate_fwd", "dmf_ln_modulate_bwd", "dmf_adaln_bwd_workspace_bytes",
     "dmf_gate_residual_fwd", "dmf_gate_residual_bwd",
+    "dmf_step_tail",
 )
 ADALN_BF16, ADALN_F32 = 0, 2
 
@@ -126,6 +127,19 @@ class GateResidualBwdArgs(C.Structure):
     ]
 
 
+class StepTailArgs(C.Structure):
+    """dmf_step_tail_args (include/dmf_step.h)."""
+    _fields_ = [
+        ("count", C.c_int64),
+        ("grad", C.c_void_p), ("param", C.c_void_p), ("exp_avg", C.c_void_p), ("exp_avg_sq", C.c_void_p),
+        ("ema", C.c_void_p), ("grad_norm", C.c_void_p),
+        ("max_grad_norm", C.c_float), ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float),
+        ("eps", C.c_float), ("weight_decay", C.c_float), ("step_size", C.c_float),
+        ("bias_correction2_sqrt", C.c_float), ("ema_decay", C.c_float), ("reserved", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
 class DmfAttnError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"dmf_attn: {STATUS_NAMES.get(status, status)}: {message}")
@@ -184,6 +198,8 @@ def load() -> C.CDLL:
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(args)]
+        lib.dmf_step_tail.restype = C.c_int
+        lib.dmf_step_tail.argtypes = [C.POINTER(StepTailArgs)]
         lib.dmf_adaln_bwd_workspace_bytes.restype = C.c_size_t
         lib.dmf_adaln_bwd_workspace_bytes.argtypes = [C.c_int32] * 3
         got = lib.dmf_attn_abi_version()

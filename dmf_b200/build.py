@@ -18,7 +18,7 @@ CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libdmf_attn.so"
 
-SOURCES = ["dmf_attn.cu", "dmf_adaln.cu"]
+SOURCES = ["dmf_attn.cu", "dmf_adaln.cu", "dmf_step.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

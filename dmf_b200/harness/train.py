@@ -23,8 +23,14 @@ place of the DDP wrapper, in one of two ways:
 * ``overlap=False``: a single all-reduce of the whole buffer after the last micro-batch.
 
 Either way the mean over ranks is taken by scaling the loss by 1 / world size before backward (a
-power of two on 2, 4, 8 GPUs: exact), not by a pass over the reduced buffer, and the clipping
-coefficient is applied inside the fused AdamW kernel instead of by a pass of its own.
+power of two on 2, 4, 8 GPUs: exact), not by a pass over the reduced buffer.  With ``fused_tail=True``
+(default) parameters, AdamW moments and EMA copies live in flat buffers as well and the rest of the
+step - clipping, AdamW, EMA, zeroing of the gradients - is one norm reduction plus ONE kernel
+(``dmf_step_tail``); otherwise torch's fused AdamW (with the clipping coefficient as its grad_scale)
+and two foreach EMA calls.
+
+Graphs that hold captured collectives must be released (drop the TrainState) before the process
+group is destroyed; the teardown otherwise waits for them.
 """
 
 from __future__ import annotations
@@ -38,6 +44,7 @@ import torch.distributed as dist
 from torch.nn.parallel import DistributedDataParallel as DDP
 
 from .. import ops as _ops
+from ..step import FlatAdamW
 from .loss import DMFLoss
 from .model import build_dmft
 
@@ -72,12 +79,15 @@ class TrainState:
     pool: object | None = None              # memory pool shared by this state's graphs (they never run concurrently)
     timing: dict | None = None              # set to {} to have train_step record CUDA events around its phases
     steps_done: int = 0
+    flat_param: torch.Tensor | None = None  # graphs + fused tail: all trainable parameters, one buffer (p.data are views)
+    flat_ema: torch.Tensor | None = None    # ... and their EMA copies
+    flat_opt: FlatAdamW | None = None       # ... and the AdamW moments; None: torch's fused AdamW + foreach EMA
 
 
 def build_train_state(device, *, name: str = "DMFT-XL/2", input_size: int = 32, dmf_depth: int = 20,
                       attn_func: str = "fa3", qk_norm: bool = False, seed: int = 0, lr: float = 1e-4,
                       zero_init: bool = True, graphs: bool = False, overlap: bool = True,
-                      n_buckets: int = 8) -> TrainState:
+                      n_buckets: int = 8, fused_tail: bool = True) -> TrainState:
     torch.manual_seed(seed)  # same initial weights on every rank
     model = build_dmft(name, input_size=input_size, dmf_depth=dmf_depth, use_logvar=True, num_classes=1000,
                        attn_func=attn_func, qk_norm=qk_norm)
@@ -106,6 +116,20 @@ def build_train_state(device, *, name: str = "DMFT-XL/2", input_size: int = 32, 
         state.comm_stream = torch.cuda.Stream(device=device)
         # the clipping coefficient reaches the fused AdamW kernel as its grad_scale (it divides by it)
         opt.grad_scale = torch.ones((), dtype=torch.float32, device=device)
+        if fused_tail:
+            # parameters and their EMA copies move into flat buffers too (each tensor becomes a view), so that clipping,
+            # AdamW, the EMA and the zeroing of the gradients are one pass of one kernel over five buffers
+            def flatten(tensors):
+                flat = torch.empty(sum(t.numel() for t in tensors), dtype=torch.float32, device=device)
+                o = 0
+                for t in tensors:
+                    flat[o:o + t.numel()].copy_(t.detach().reshape(-1))
+                    t.data = flat[o:o + t.numel()].view_as(t)
+                    o += t.numel()
+                return flat
+            state.flat_param = flatten(params)
+            state.flat_ema = flatten([q for q, p in zip(ema.parameters(), model.parameters()) if p.requires_grad])
+            state.flat_opt = FlatAdamW(state.flat_param, lr=lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0)
     return state
 
 
@@ -250,13 +274,20 @@ def _train_step_graphed(state: TrainState, micro_batches, max_grad_norm, ema_dec
     _mark(state, "step_start")
     total = accumulate_graphed(state, micro_batches, autocast_dtype)
     flat = state.flat_grad
-    # clip_grad_norm_ on the flat buffer without a host sync and without a pass of its own: the coefficient
-    # min(1, max_norm / (norm + 1e-6)) goes to the fused AdamW kernel, which divides every gradient by grad_scale
-    coef = torch.clamp(max_grad_norm / (flat.norm(2) + 1e-6), max=1.0)
-    state.opt.grad_scale.copy_(1.0 / coef)
-    state.opt.step()
-    flat.zero_()                                # p.grad stay views of the buffer
-    update_ema(state.ema, state.model, ema_decay)
+    if state.flat_opt is not None:
+        # one reduction for the norm, then clip + AdamW + EMA + zeroing of the gradients in one pass over the buffers
+        state.flat_opt.step_tail(flat, state.flat_param, state.flat_ema, flat.norm(2), max_grad_norm=max_grad_norm,
+                                 ema_decay=ema_decay)
+        for b_ema, b in zip(state.ema.buffers(), state.model.buffers()):
+            b_ema.copy_(b)
+    else:
+        # clip_grad_norm_ on the flat buffer without a host sync and without a pass of its own: the coefficient
+        # min(1, max_norm / (norm + 1e-6)) goes to the fused AdamW kernel, which divides every gradient by grad_scale
+        coef = torch.clamp(max_grad_norm / (flat.norm(2) + 1e-6), max=1.0)
+        state.opt.grad_scale.copy_(1.0 / coef)
+        state.opt.step()
+        flat.zero_()                            # p.grad stay views of the buffer
+        update_ema(state.ema, state.model, ema_decay)
     _mark(state, "tail_done")
     state.steps_done += 1
     _ops.poll_device_status(state.device)       # a kernel that gave up a wait is reported one step later, no sync

@@ -152,3 +152,25 @@ def test_lazy_rescale_variant_is_the_same_function_and_shows_why_it_exists():
     oe, doe, _ = orc.attn_jvp_online(q, k, v, tq, tk, tv, emulate_bf16=True)
     assert orc.rel_l2(ob, o_ref) < 6e-3 and orc.rel_l2(dob, do_ref) < 6e-3
     assert 1e-5 < orc.max_rel(ob, oe) < 1e-2
+
+
+def test_step_tail_oracle_matches_the_library_calls_of_the_reference_step():
+    """clip_grad_norm_ + torch.optim.AdamW + the EMA formula, three steps on CPU, against the fp64 restatement."""
+    from oracle import step_oracle as so
+    g = torch.Generator().manual_seed(3)
+    p = torch.nn.Parameter(torch.randn(1000, generator=g))
+    ema = p.detach().clone()
+    opt = torch.optim.AdamW([p], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.05, eps=1e-8)
+    po, m, v, eo = p.detach().double().clone(), torch.zeros(1000).double(), torch.zeros(1000).double(), ema.double().clone()
+    for t in range(1, 4):
+        grad = torch.randn(1000, generator=g) * (3.0 if t == 2 else 0.01)     # one step clips, the others do not
+        p.grad = grad.clone()
+        torch.nn.utils.clip_grad_norm_([p], 1.0)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        ema.mul_(0.999).add_(p.detach(), alpha=1 - 0.999)
+        po, m, v, eo = so.step_tail(grad, po, m, v, eo, step=t, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.05,
+                                    max_grad_norm=1.0, ema_decay=0.999)
+        assert orc.max_rel(p.detach(), po) < 1e-6 and orc.max_rel(ema, eo) < 1e-6
+        st = opt.state[p]
+        assert orc.max_rel(st["exp_avg"], m) < 1e-6 and orc.max_rel(st["exp_avg_sq"], v) < 1e-6
