@@ -262,18 +262,9 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
             bulk_load_1d(s_lse + step * 512, p.lse + off, 512, fb);
             DMF_TRACE_EVENT(0, 1 + 3 * step);
           }
-          // the forward output of the tile, for delta (one buffer: freed when the P warps have read it)
-          ok = wait(TR::kBarOEmpty, ((2u * hcnt + static_cast<uint32_t>(step)) & 1u) ^ 1u);
-          if (!ok) break;
-          {
-            const uint32_t of = bar(TR::kBarOFull);
-            mbar_arrive_expect_tx(of, TR::kTileBytes);
-            tma_load_4d(s_o, &p.o_main, of, 0, q0, h, b);
-            if constexpr (TAIL > 0) tma_load_4d(s_o + TR::kMainBytes, &p.o_tail, of, 64, q0, h, b);
-            DMF_TRACE_EVENT(0, 2 + 3 * step);
-          }
           if (step == 0) {
-            // K_r, V_r: free when the last products of the previous head (those of its step 1) are complete
+            // K_r, V_r next (the first product of the head needs K and the step-0 query tile; the forward output, for
+            // delta, is needed two thousand cycles later): free when the last products of the previous head are complete
             ok = wait(TR::kBarXEmpty + 1, ph ^ 1u);
             if (!ok) break;
             const uint32_t fb = bar(TR::kBarKVFull);
@@ -286,6 +277,16 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
               tma_load_4d(s_kv + TR::kTileBytes + TR::kMainBytes, &p.v_tail, fb, 64, k0, h, b);
             }
             DMF_TRACE_EVENT(0, 3);
+          }
+          // the forward output of the tile, for delta (one buffer: freed when the P warps have read it)
+          ok = wait(TR::kBarOEmpty, ((2u * hcnt + static_cast<uint32_t>(step)) & 1u) ^ 1u);
+          if (!ok) break;
+          {
+            const uint32_t of = bar(TR::kBarOFull);
+            mbar_arrive_expect_tx(of, TR::kTileBytes);
+            tma_load_4d(s_o, &p.o_main, of, 0, q0, h, b);
+            if constexpr (TAIL > 0) tma_load_4d(s_o + TR::kMainBytes, &p.o_tail, of, 64, q0, h, b);
+            DMF_TRACE_EVENT(0, 2 + 3 * step);
           }
         }
       }
