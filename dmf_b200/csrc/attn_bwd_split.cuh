@@ -279,9 +279,9 @@ attn_bwd_split_kernel(const __grid_constant__ BwdParams p) {
           // reads its own row, 16 bytes at a time, at the swizzled position of each chunk
           ok = wait(TR::kBarOFull, tcnt & 1u);
           if (ok) ok = wait(TR::kBarRFull, tcnt & 1u);
-          if (!ok) break;
           const uint8_t* do_tile = smem + TR::kTileBytes;
           float acc = 0.f;
+          if (ok) {  // (a failed wait skips the work, not the meeting at the tile's end)
 #pragma unroll
           for (int c = 0; c < DPAD / 8; ++c) {
             const uint32_t off = chunk_off(c * 8);
@@ -295,12 +295,13 @@ attn_bwd_split_kernel(const __grid_constant__ BwdParams p) {
               acc = fmaf(a.y, g.y, acc);
             }
           }
-          if constexpr (TR::kOwnOTile) mbar_arrive_warp(bar(TR::kBarOEmpty));  // o has been read
-          delta = acc;
-          p.ws_delta[vi] = delta;
+            if constexpr (TR::kOwnOTile) mbar_arrive_warp(bar(TR::kBarOEmpty));  // o has been read
+            delta = acc;
+            p.ws_delta[vi] = delta;
+          }
         }
       }
-      for (int j = 0; j < J; ++j, ++gblk) {
+      for (int j = 0; ok && j < J; ++j, ++gblk) {
         const float* vstage = vec + (gblk % TR::kStages) * 256;  // DKV: column vectors of this block
         if constexpr (kDKV) {
           // the vectors arrive with the streamed tiles: observe that barrier directly before reading them
@@ -432,8 +433,11 @@ attn_bwd_split_kernel(const __grid_constant__ BwdParams p) {
           mbar_arrive_warp(bar(TR::kBarGFull));
         }
       }
-      if (!ok) break;
-      if (p_role) continue;  // the P warps go straight on to the next tile
+      if (p_role) {  // the P warps go straight on to the next tile (they take part in no hardware-barrier meeting)
+        if (!ok) break;
+        continue;
+      }
+      // a D warp whose wait gave up still goes to the meeting below, so that no other D warp is left alone there
       // ---- epilogue (D warps) -------------------------------------------------
       // the commit behind the last accumulating product of the tile also freed its ring slot
       if (ok) ok = wait(TR::kBarXEmpty + (gblk - 1u) % TR::kStages, ((gblk - 1u) / TR::kStages) & 1u);
