@@ -82,11 +82,11 @@ struct BwdFusedTraits {
   static constexpr int kOffLse = kOffXchg + kXchgBytes;          // raw lse rows as loaded, per stage
   static constexpr int kOffVec = kOffLse + kStages * 512;
   static constexpr int kOffBars = kOffVec + kStages * kVecBytes;
-  static constexpr int kBarKVFull = 0, kBarXFull = 1 /* +stage */, kBarXEmpty = 3 /* +stage */, kBarOFull = 5,
+  static constexpr int kBarKFull = 0, kBarXFull = 1 /* +stage */, kBarXEmpty = 3 /* +stage */, kBarOFull = 5,
                        kBarOEmpty = 6, kBarSFull = 7, kBarSEmpty = 8, kBarDFull = 9, kBarPFull = 10, kBarPEmpty = 11,
                        kBarGFull = 12, kBarRecvInTmem = 15, kBarAccEmpty = 16,
                        kBarXchgFull = 17, kBarX0Both = 18, kBarSendDone = 19, kBarX0Free = 20, kBarQStaged = 21,
-                       kBarKVStaged = 22, kBarStageFree = 13, kNumBars = 23;
+                       kBarKVStaged = 22, kBarStageFree = 13, kBarVFull = 23, kNumBars = 24;
   static constexpr int kSmemBytes = 1024 + kOffBars + kNumBars * 8 + 16;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
   static constexpr uint32_t kColS = 0, kColD = 128, kColP = 256, kColDK = 320, kColDV = 320 + kDPad;
@@ -267,15 +267,15 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
             // delta, is needed two thousand cycles later): free when the last products of the previous head are complete
             ok = wait(TR::kBarXEmpty + 1, ph ^ 1u);
             if (!ok) break;
-            const uint32_t fb = bar(TR::kBarKVFull);
+            // K on a barrier of its own, ahead of V: the head's first product needs only K
+            const uint32_t fk = bar(TR::kBarKFull), fv = bar(TR::kBarVFull);
             const int k0 = static_cast<int>(rank) * 128;
-            mbar_arrive_expect_tx(fb, TR::kGroupBytes);
-            tma_load_4d(s_kv, &p.k_main, fb, 0, k0, h, b);
-            tma_load_4d(s_kv + TR::kTileBytes, &p.v_main, fb, 0, k0, h, b);
-            if constexpr (TAIL > 0) {
-              tma_load_4d(s_kv + TR::kMainBytes, &p.k_tail, fb, 64, k0, h, b);
-              tma_load_4d(s_kv + TR::kTileBytes + TR::kMainBytes, &p.v_tail, fb, 64, k0, h, b);
-            }
+            mbar_arrive_expect_tx(fk, TR::kTileBytes);
+            tma_load_4d(s_kv, &p.k_main, fk, 0, k0, h, b);
+            if constexpr (TAIL > 0) tma_load_4d(s_kv + TR::kMainBytes, &p.k_tail, fk, 64, k0, h, b);
+            mbar_arrive_expect_tx(fv, TR::kTileBytes);
+            tma_load_4d(s_kv + TR::kTileBytes, &p.v_main, fv, 0, k0, h, b);
+            if constexpr (TAIL > 0) tma_load_4d(s_kv + TR::kTileBytes + TR::kMainBytes, &p.v_tail, fv, 64, k0, h, b);
             DMF_TRACE_EVENT(0, 3);
           }
           // the forward output of the tile, for delta (one buffer: freed when the P warps have read it)
@@ -318,7 +318,7 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
       const uint32_t q0_tile = s_x, do0_tile = s_x + TR::kTileBytes;
       const uint32_t q1_tile = s_x + TR::kGroupBytes, do1_tile = q1_tile + TR::kTileBytes;
       // ---- S_0, dP_0, S_1 ----
-      ok = wait(TR::kBarKVFull, ph) && wait(TR::kBarXFull + 0, ph);
+      ok = wait(TR::kBarKFull, ph) && wait(TR::kBarXFull + 0, ph);
       if (ok && hcnt > 0) ok = wait_s_empty(3u * hcnt - 1u);   // the previous head's first dQ partial has been read
       if (!ok) break;
       tc_fence_after_sync();
@@ -327,6 +327,9 @@ attn_bwd_fused_kernel(const __grid_constant__ BwdFusedParams p) {
       commit(TR::kBarSFull);
       DMF_TRACE_EVENT(1, 11);
       // (the dP columns are free: the D warps had read dP_1 of the previous head before its last products were issued)
+      ok = wait(TR::kBarVFull, ph);
+      if (!ok) break;
+      tc_fence_after_sync();
       issue_qk<TAIL, TR>(leader, t_d, v_tile, do0_tile, idesc_qk, false);    // dP_0^T = V dO_0^T
       commit(TR::kBarDFull);
       DMF_TRACE_EVENT(1, 12);
