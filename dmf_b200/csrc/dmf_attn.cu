@@ -15,6 +15,7 @@
 #include "attn_bwd.cuh"
 #include "attn_bwd_fused.cuh"
 #include "attn_bwd_split.cuh"
+#include "attn_bwd_stream.cuh"
 #include "attn_fwd.cuh"
 #include "attn_fwd_pair.cuh"
 #include "rmsnorm.cuh"
@@ -357,10 +358,27 @@ int run_fwd(const dmf_attn_fwd_args* a, bool dual, bool f32out = false) {
 
 // ---- backward ----
 
+// The part of the workspace every backward kernel needs: -lse*log2(e) and delta = rowsum(dO*O), one float per
+// query row each.  A call is valid with this much.
+size_t bwd_workspace_min_bytes(int batch, int lq, int heads) {
+  return 2 * sizeof(float) * static_cast<size_t>(batch) * heads * lq;
+}
+
+// Offset of the fp32 dQ accumulator of the one-pass long-sequence kernel behind the two rows.
+size_t bwd_stream_acc_offset(int batch, int lq, int heads) {
+  return (bwd_workspace_min_bytes(batch, lq, heads) + 255) & ~static_cast<size_t>(255);
+}
+
+bool bwd_uses_fused(int tail, int seqlen_q, int seqlen_kv);
+bool bwd_stream_applies(int tail, int seqlen_q, int seqlen_kv);
+
+// What dmf_attn_bwd_workspace_bytes reports: where the one-pass long-sequence kernel applies, room for its dQ
+// accumulator too (with less, dmf_attn_bwd runs the two-launch kernels).
 size_t bwd_workspace_bytes(int batch, int lq, int lkv, int heads, int d) {
   if (check_dims(batch, lq, lkv, heads, d, DMF_ATTN_BF16) != DMF_ATTN_OK) return 0;
-  // -lse*log2(e) and delta = rowsum(dO*O), one float per query row each
-  return 2 * sizeof(float) * static_cast<size_t>(batch) * heads * lq;
+  if (bwd_stream_applies(tail_of(d), lq, lkv))
+    return bwd_stream_acc_offset(batch, lq, heads) + sizeof(float) * static_cast<size_t>(batch) * heads * lq * d;
+  return bwd_workspace_min_bytes(batch, lq, heads);
 }
 
 int validate_bwd(const dmf_attn_bwd_args* a) {
@@ -372,7 +390,7 @@ int validate_bwd(const dmf_attn_bwd_args* a) {
   const dmf_attn_tensor* ts[] = {&a->dout, &a->q, &a->k, &a->v, &a->o, &a->dq, &a->dk, &a->dv};
   for (const dmf_attn_tensor* t : ts)
     if ((st = check_tensor(*t, 2)) != DMF_ATTN_OK) return st;
-  const size_t need = bwd_workspace_bytes(a->batch, a->seqlen_q, a->seqlen_kv, a->heads, a->head_dim);
+  const size_t need = bwd_workspace_min_bytes(a->batch, a->seqlen_q, a->heads);
   if (a->workspace == nullptr || a->workspace_bytes < need) return DMF_ATTN_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(a->workspace) & 15u) != 0) return DMF_ATTN_ERR_ALIGN;
   return DMF_ATTN_OK;
@@ -503,9 +521,97 @@ int run_bwd_fused(const dmf_attn_bwd_args* a, int tail, int sm_count) {
                    : launch_bwd_fused_inst<__half, 16>(p, clusters, stream);
 }
 
+// ---- backward in one pass, long sequences (head_dim <= 80): key tiles resident, dQ summed with atomics ----
+
+// DMF_ATTN_BWD_STREAM=0 in the environment keeps the two-launch backward (for comparisons, and for callers that
+// need a dQ that is reproducible bit for bit).
+bool bwd_stream_enabled() {
+  static const bool enabled = [] {
+    const char* e = std::getenv("DMF_ATTN_BWD_STREAM");
+    return e == nullptr || e[0] != '0';
+  }();
+  return enabled;
+}
+
+bool bwd_stream_applies(int tail, int seqlen_q, int seqlen_kv) {
+  return tail >= 0 && tail <= 16 && !bwd_uses_fused(tail, seqlen_q, seqlen_kv) && bwd_stream_enabled();
+}
+
+template <typename T, int TAIL>
+int launch_bwd_stream_inst(const BwdStreamParams& p, const dmf_attn_bwd_args* a, int sm_count, cudaStream_t stream) {
+  using TR = BwdStreamTraits<TAIL>;
+  auto kernel = attn_bwd_stream_kernel<T, TAIL>;
+  auto convert = bwd_dq_convert_kernel<T>;
+  const int convert_smem = (p.head_dim / 4) * 128 * 16;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(convert, cudaFuncAttributeMaxDynamicSharedMemorySize, convert_smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_LAUNCH;
+  }
+  // rows of the pre-kernel's block: 32 positions of all heads, fewer when that does not fit 48 KB of shared memory
+  int lrows = 32;
+  while (lrows > 1 && static_cast<size_t>(lrows) * p.heads * (p.head_dim / 8) * sizeof(float) > 48 * 1024) lrows /= 2;
+  const size_t delta_smem = static_cast<size_t>(lrows) * p.heads * (p.head_dim / 8) * sizeof(float);
+  if (delta_smem > 48 * 1024) return DMF_ATTN_ERR_SHAPE;
+  const int64_t want = static_cast<int64_t>(p.batch) * (p.seqlen_q / lrows);
+  const int delta_grid = static_cast<int>(want < 16 * sm_count ? want : 16 * sm_count);
+  bwd_delta_kernel<T><<<delta_grid, 256, delta_smem, stream>>>(
+      static_cast<const T*>(a->o.ptr), static_cast<const T*>(a->dout.ptr), a->lse, const_cast<float*>(p.ndelta),
+      const_cast<float*>(p.nlse2), p.batch, p.seqlen_q, p.heads, p.head_dim, lrows, a->o.stride_b, a->o.stride_l,
+      a->o.stride_h, a->dout.stride_b, a->dout.stride_l, a->dout.stride_h);
+  const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
+  kernel<<<grid, kBwdStreamThreads, TR::kSmemBytes, stream>>>(p);
+  convert<<<p.batch * p.heads * p.steps, 256, convert_smem, stream>>>(
+      p.dq_acc, static_cast<T*>(a->dq.ptr), p.heads, p.head_dim, p.steps, a->dq.stride_b, a->dq.stride_l,
+      a->dq.stride_h, p.scale);
+  return cudaGetLastError() == cudaSuccess ? DMF_ATTN_OK : DMF_ATTN_ERR_LAUNCH;
+}
+
+int run_bwd_stream(const dmf_attn_bwd_args* a, int tail, int sm_count) {
+  const int B = a->batch, H = a->heads, D = a->head_dim, Lq = a->seqlen_q, Lk = a->seqlen_kv, dt = a->dtype;
+  BwdStreamParams p;
+  std::memset(&p, 0, sizeof(p));
+  int st;
+  const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_32B;  // tiles as blocks of 16 columns
+  if ((st = make_map(&p.q, a->q, dt, B, Lq, H, D, 16, 128, sw)) != DMF_ATTN_OK) return st;
+  if ((st = make_map(&p.dout, a->dout, dt, B, Lq, H, D, 16, 128, sw)) != DMF_ATTN_OK) return st;
+  if ((st = make_map(&p.k, a->k, dt, B, Lk, H, D, 16, 128, sw)) != DMF_ATTN_OK) return st;
+  if ((st = make_map(&p.v, a->v, dt, B, Lk, H, D, 16, 128, sw)) != DMF_ATTN_OK) return st;
+  if ((st = make_map(&p.dk, a->dk, dt, B, Lk, H, D, 16, 128, sw)) != DMF_ATTN_OK) return st;
+  if ((st = make_map(&p.dv, a->dv, dt, B, Lk, H, D, 16, 128, sw)) != DMF_ATTN_OK) return st;
+  float* ws = static_cast<float*>(a->workspace);
+  p.nlse2 = ws;
+  p.ndelta = ws + static_cast<size_t>(B) * H * Lq;
+  p.dq_acc = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + bwd_stream_acc_offset(B, Lq, H));
+  p.status_word = a->status_word;
+  p.batch = B; p.heads = H; p.head_dim = D; p.seqlen_q = Lq; p.seqlen_kv = Lk;
+  p.tiles_per_bh = Lk / 128;
+  p.num_tiles = B * H * p.tiles_per_bh;
+  p.steps = Lq / 128;
+  p.scale = a->softmax_scale;
+  p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (cudaMemsetAsync(p.dq_acc, 0, sizeof(float) * static_cast<size_t>(B) * H * Lq * D, stream) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DMF_ATTN_ERR_LAUNCH;
+  }
+  if (dt == DMF_ATTN_BF16)
+    return tail == 0 ? launch_bwd_stream_inst<__nv_bfloat16, 0>(p, a, sm_count, stream)
+                     : launch_bwd_stream_inst<__nv_bfloat16, 16>(p, a, sm_count, stream);
+  return tail == 0 ? launch_bwd_stream_inst<__half, 0>(p, a, sm_count, stream)
+                   : launch_bwd_stream_inst<__half, 16>(p, a, sm_count, stream);
+}
+
 void bwd_kernel_name(const char* t, int tail, int seqlen_q, int seqlen_kv, char* buf, size_t len) {
   if (bwd_uses_fused(tail, seqlen_q, seqlen_kv)) {
     std::snprintf(buf, len, "attn_bwd_fused_kernel<%s, TAIL=%d> (one pass, cluster of two CTAs per head)", t, tail);
+    return;
+  }
+  if (bwd_stream_applies(tail, seqlen_q, seqlen_kv)) {
+    std::snprintf(buf, len,
+                  "bwd_delta_kernel<%s> + attn_bwd_stream_kernel<%s, TAIL=%d> (one pass, dQ by atomics) + "
+                  "bwd_dq_convert_kernel<%s>",
+                  t, t, tail, t);
     return;
   }
   const char* name = (tail <= 32 && bwd_split_enabled()) ? "attn_bwd_split_kernel" : "attn_bwd_kernel";
@@ -523,6 +629,10 @@ int run_bwd(const dmf_attn_bwd_args* a) {
   // two-tile sequences: the one-pass kernel (it needs no workspace; lse rows are fetched with 16-byte bulk copies)
   if (bwd_uses_fused(tail, Lq, Lk) && (reinterpret_cast<uintptr_t>(a->lse) & 15u) == 0)
     return run_bwd_fused(a, tail, sm_count);
+  // long sequences at head_dim <= 80, when the workspace has room for the fp32 dQ accumulator: one pass
+  if (bwd_stream_applies(tail, Lq, Lk) && a->workspace_bytes >= bwd_workspace_bytes(B, Lq, Lk, H, D) &&
+      (reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0)
+    return run_bwd_stream(a, tail, sm_count);
 
   BwdParams p;
   std::memset(&p, 0, sizeof(p));
@@ -620,6 +730,9 @@ int run_bwd_static(const dmf_attn_bwd_args* a) {
   float* scratch = nullptr;
   if ((st = static_scratch_ptr(&scratch)) != DMF_ATTN_OK) return st;
   local.workspace = scratch;
+  // only the two rows per query: the call then never takes the one-pass long-sequence kernel, whose fp32 dQ
+  // accumulator does not fit the scratch array for most shapes, and stays reproducible bit for bit
+  local.workspace_bytes = bwd_workspace_min_bytes(a->batch, a->seqlen_q, a->heads);
   return run_bwd(&local);
 }
 

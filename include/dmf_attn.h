@@ -86,9 +86,18 @@ typedef struct dmf_attn_fwd_args {
 /*
  * Arguments of the primal backward.  grads of lse and of the tangent output are
  * not inputs: the reference drops them (stop-gradient on the tangent).
- * workspace: device memory of at least dmf_attn_bwd_workspace_bytes(); its
- * contents on entry do not matter (the first pass writes every word the second
- * pass reads; nothing is accumulated in it).
+ * workspace: device memory, 16-byte aligned, of at least 8 * batch * heads *
+ * seqlen_q bytes (two fp32 rows per query); its contents on entry do not matter.
+ * dmf_attn_bwd_workspace_bytes() reports what the fastest kernel for the problem
+ * wants: for sequences of more than two tiles at head_dim <= 80 that is room for
+ * an fp32 dQ accumulator (4 * batch * heads * seqlen_q * head_dim bytes) behind
+ * the two rows, with the workspace 256-byte aligned.  That kernel visits every
+ * 128 x 128 block of scores once and sums a query tile's dQ over the key tiles
+ * with fp32 atomics, so the last bits of dq depend on the order the blocks
+ * finished in (dk and dv do not; the FlashAttention backward the reference
+ * calls behaves the same way with deterministic=False).  With a workspace
+ * smaller than reported, or DMF_ATTN_BWD_STREAM=0 in the environment, the call
+ * runs the two-launch kernels, whose results are reproducible bit for bit.
  */
 typedef struct dmf_attn_bwd_args {
   int32_t batch;
@@ -142,7 +151,8 @@ int dmf_attn_fwd(const dmf_attn_fwd_args* args);
  */
 int dmf_attn_bwd(const dmf_attn_bwd_args* args);
 
-/* Bytes of workspace dmf_attn_bwd needs for this problem size (0 on bad sizes). */
+/* Bytes of workspace the fastest kernel of dmf_attn_bwd wants for this problem size (0 on bad sizes);
+ * see dmf_attn_bwd_args for the minimum a call is valid with. */
 size_t dmf_attn_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t seqlen_kv,
                                     int32_t heads, int32_t head_dim);
 
@@ -156,10 +166,11 @@ size_t dmf_attn_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t seq
  * a framework whose allocator it cannot reach, a service running inside a fixed
  * memory reservation, a step that must not call cudaMalloc because that call
  * synchronises the whole device.  For them this entry point does exactly what
- * dmf_attn_bwd does, but takes its scratch (two floats per query row) from a
- * fixed array that lives inside the library image instead of args->workspace,
- * which is ignored together with args->workspace_bytes.  It calls no
- * cudaMalloc, cudaFree or any other allocating routine.
+ * dmf_attn_bwd does with its minimal workspace (two floats per query row; the
+ * kernels whose results are reproducible bit for bit), but takes that scratch
+ * from a fixed array that lives inside the library image instead of
+ * args->workspace, which is ignored together with args->workspace_bytes.  It
+ * calls no cudaMalloc, cudaFree or any other allocating routine.
  *
  * Limit: batch * heads * seqlen_q <= DMF_ATTN_STATIC_MAX_ROWS (1,048,576 rows,
  * i.e. 8 MiB of device memory, held by every GPU that loads the library until

@@ -53,9 +53,12 @@ def fwd(q, k, v, tq=None, tk=None, tv=None, scale=None, expect=0, packed_out=Fal
     return o, to, lse, st
 
 
-def bwd(dout, q, k, v, o, lse, scale=None, expect=0, packed_out=False):
+def bwd(dout, q, k, v, o, lse, scale=None, expect=0, packed_out=False, min_workspace=False):
     """dmf_attn_bwd.  Returns (dq, dk, dv, status).
-    packed_out (self-attention shapes only): dq, dk, dv are strided views of one (B, L, 3, H, D) buffer."""
+    packed_out (self-attention shapes only): dq, dk, dv are strided views of one (B, L, 3, H, D) buffer.
+    min_workspace: pass only the two fp32 rows per query every kernel needs (8 * B * H * Lq bytes) instead of
+    what dmf_attn_bwd_workspace_bytes reports; the long-sequence one-pass kernel, which wants an fp32 dQ
+    accumulator behind them, then leaves the call to the two-launch kernels."""
     B, Lq, H, D = q.shape
     dev = q.device
     nan = float("nan")
@@ -69,6 +72,9 @@ def bwd(dout, q, k, v, o, lse, scale=None, expect=0, packed_out=False):
         dv = torch.full(v.shape, nan, dtype=q.dtype, device=dev)
     lib = _lib.load()
     nbytes = lib.dmf_attn_bwd_workspace_bytes(B, Lq, k.shape[1], H, D)
+    if min_workspace:
+        assert nbytes >= 8 * B * H * Lq
+        nbytes = 8 * B * H * Lq
     ws = torch.full((max(nbytes, 16),), 0xFF, dtype=torch.uint8, device=dev)  # garbage on purpose
     sw = status_word(dev)
     a = _lib.BwdArgs()

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 from oracle import attn_jvp_oracle as orc
+from dmf_b200 import _lib
 from tests import _cabi
 from tests.conftest import GOLDEN
 from tests.golden.make_golden import CASES
@@ -73,6 +74,41 @@ def test_backward_many_tiles_and_determinism():
     _check((dq, dk, dv), orc.attn_bwd_closed_form(q.float(), k.float(), v.float(), dout.float()))
     _, _, dq2, dk2, dv2 = _fwd_bwd((q, k, v), dout)
     assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)  # no atomics anywhere
+
+
+def test_long_sequence_one_pass_backward():
+    """Lengths beyond two tiles at head_dim <= 80 go to the one-pass kernel (key tile resident, dQ summed over the
+    key tiles with fp32 atomics) when the workspace has room for its accumulator: several key tiles per CTA
+    (320 tiles on 148 SMs), all three gradients against the oracle; dK and dV bit-identical from run to run, dQ up
+    to the order of its fp32 additions; and the two-launch kernels, which the minimal workspace selects, agree."""
+    assert "stream" in _lib.kernel_name("bwd", 1024, 1024, 72)
+    assert "stream" not in _lib.kernel_name("bwd", 256, 256, 72)       # two tiles: the cluster kernel
+    assert "stream" not in _lib.kernel_name("bwd", 1024, 1024, 128)    # head_dim above 80: two launches
+    q, k, v, _, _, _, dout = (x.bfloat16() for x in orc.make_inputs(2, 1024, 20, 72, seed=31, n_extra=1))
+    ref = orc.attn_bwd_closed_form(q.float(), k.float(), v.float(), dout.float())
+    qd, kd, vd, dd = (x.to(DEV) for x in (q, k, v, dout))
+    o, _, lse, _ = _cabi.fwd(qd, kd, vd)
+    dq, dk, dv, _ = _cabi.bwd(dd, qd, kd, vd, o, lse)
+    _check((dq.cpu(), dk.cpu(), dv.cpu()), ref)
+    dq2, dk2, dv2, _ = _cabi.bwd(dd, qd, kd, vd, o, lse)
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    assert orc.rel_l2(dq2.float().cpu(), dq.float().cpu()) < 1e-3      # same sums, another order
+    dq3, dk3, dv3, _ = _cabi.bwd(dd, qd, kd, vd, o, lse, min_workspace=True)
+    _check((dq3.cpu(), dk3.cpu(), dv3.cpu()), ref)
+    dq4, dk4, dv4, _ = _cabi.bwd(dd, qd, kd, vd, o, lse, min_workspace=True)
+    assert torch.equal(dq3, dq4) and torch.equal(dk3, dk4) and torch.equal(dv3, dv4)   # no atomics there
+    for a, b in ((dq, dq3), (dk, dk3), (dv, dv3)):
+        assert orc.rel_l2(a.float().cpu(), b.float().cpu()) < 6e-3     # two roundings to bf16 apart
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 128, 1, 64), (1, 384, 128, 1, 80), (1, 128, 640, 2, 72), (2, 640, 384, 3, 64)])
+def test_long_sequence_one_pass_backward_ragged_lengths_fp16(shape):
+    """One tile, one step per tile, more steps than tiles and the reverse, in fp16."""
+    B, Lq, Lk, H, D = shape
+    q, _, _, _, _, _, dout = (x.half() for x in orc.make_inputs(B, Lq, H, D, seed=Lq + Lk, n_extra=1))
+    _, k, v, _, _, _ = (x.half() for x in orc.make_inputs(B, Lk, H, D, seed=Lq + Lk + 1))
+    _, _, dq, dk, dv = _fwd_bwd((q, k, v), dout)
+    _check((dq, dk, dv), orc.attn_bwd_closed_form(q.float(), k.float(), v.float(), dout.float()), tol=1e-3)
 
 
 @pytest.mark.parametrize("name", list(CASES))

@@ -59,6 +59,19 @@ def test_validation_accepts_reference_layouts():
     assert lib.dmf_attn_validate_fwd(C.byref(a), 0) == 0
 
 
+def test_backward_workspace_sizes():
+    """Two fp32 rows per query for every backward kernel; where the long-sequence one-pass kernel applies (more
+    than two tiles in a length, head_dim <= 80), an fp32 dQ accumulator behind them, 256-byte aligned."""
+    lib = _lib.load()
+    rows = lambda B, H, L: 8 * B * H * L
+    assert lib.dmf_attn_bwd_workspace_bytes(256, 256, 256, 16, 72) == rows(256, 16, 256)     # two tiles: cluster kernel
+    assert lib.dmf_attn_bwd_workspace_bytes(4, 1024, 1024, 16, 128) == rows(4, 16, 1024)     # head_dim above 80
+    assert lib.dmf_attn_bwd_workspace_bytes(64, 1024, 1024, 16, 72) == rows(64, 16, 1024) + 4 * 64 * 16 * 1024 * 72
+    assert lib.dmf_attn_bwd_workspace_bytes(1, 128, 384, 3, 64) == 3072 + 4 * 3 * 128 * 64   # 3072 is already aligned
+    assert lib.dmf_attn_bwd_workspace_bytes(1, 128, 384, 1, 64) == 1024 + 4 * 128 * 64
+    assert lib.dmf_attn_bwd_workspace_bytes(1, 100, 128, 1, 64) == 0                         # not a valid problem
+
+
 @pytest.mark.parametrize("field,value,status", [
     ("dtype", 7, 2),
     ("head_dim", 48, 3), ("head_dim", 76, 3), ("head_dim", 136, 3),
