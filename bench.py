@@ -278,6 +278,13 @@ def _attn_roofline(op, B, L, H, D, ms, peaks):
             "frac": gbs / peaks["hbm_gbs"] if hbm_bound else tf / peaks["tflops"]}
 
 
+def _launches_per_call(op: str, L: int, D: int) -> int:
+    """Kernels of this library that one call of the op launches (a memset of the one-pass backward is not counted)."""
+    if op != "bwd":
+        return 1
+    return _kernel_name("bwd", D, L).count(" + ") + 1      # the entry point names its kernels joined by " + "
+
+
 def _secondary(dev, peaks, steps):
     """The other kernels of the path at the shapes the model runs them at, a second or so each: value and fraction of
     the roofline that bounds each (of the measured peaks)."""
@@ -615,7 +622,7 @@ def run_ours(args):
             "op": op,
             "cpu_baseline": cpu_base,
             "e2e": e2e,
-            "gpu_launches": args.steps * (2 if op == "bwd" else 1),
+            "gpu_launches": args.steps * _launches_per_call(op, L, D),
             "clocks": clocks,
             "secondary": secondary,
             "gpu_comparator": comparator,
