@@ -125,13 +125,19 @@ def _pin_to_gpu_numa_node(dev_index):
 class ClockSampler(threading.Thread):
     """Reads (never sets) SM clock and throttle reasons through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.005):
+    def __init__(self, index: int, period_s: float = 0.002):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz, self.uuid = [], set(), None, None
         self._stop_evt = threading.Event()
         self.active = threading.Event()
+        self.ready = threading.Event()
         self.error = None
+
+    def start(self):
+        """Start the thread and wait until NVML answers (its first call can take longer than a short timed region)."""
+        super().start()
+        self.ready.wait(timeout=15)
 
     def run(self):
         try:
@@ -139,6 +145,8 @@ class ClockSampler(threading.Thread):
             nv.nvmlInit()
             h, self.uuid = _nvml_handle(nv, self.index)
             self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)  # the first read is the slow one
+            self.ready.set()
             names = {
                 "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
@@ -156,6 +164,8 @@ class ClockSampler(threading.Thread):
                 time.sleep(self.period)
         except Exception as e:  # NVML missing: report, do not fail the bench
             self.error = repr(e)
+        finally:
+            self.ready.set()
 
     def stop(self):
         self._stop_evt.set()
