@@ -111,6 +111,37 @@ def test_long_sequence_one_pass_backward_ragged_lengths_fp16(shape):
     _check((dq, dk, dv), orc.attn_bwd_closed_form(q.float(), k.float(), v.float(), dout.float()), tol=1e-3)
 
 
+@pytest.mark.parametrize("cfg", ["C2", "C3"])
+def test_backward_full_size_properties(cfg):
+    """At the full benchmark sizes: batch slices against the oracle, the one-pass kernel of the shape against the
+    two-launch kernels (what the minimal workspace selects), linearity of all three gradients in dout (a power of two
+    scales bf16 exactly), and dk / dv bit-identical between runs."""
+    B, L, H, D, _, qkn = orc.CONFIGS[cfg]
+    gen = torch.Generator(device=DEV).manual_seed(1)
+    qkv = torch.randn(B, L, 3, H, D, device=DEV, dtype=torch.bfloat16, generator=gen)
+    dout = torch.randn(B, L, H, D, device=DEV, dtype=torch.bfloat16, generator=gen)
+    if qkn:
+        nrm = lambda x: (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)).to(x.dtype)
+        q, k = nrm(qkv[:, :, 0]), nrm(qkv[:, :, 1])
+    else:
+        q, k = qkv[:, :, 0], qkv[:, :, 1]
+    v = qkv[:, :, 2]
+    o, _, lse, _ = _cabi.fwd(q, k, v)
+    dq, dk, dv, _ = _cabi.bwd(dout, q, k, v, o, lse)
+    for b in (0, B - 1):
+        refs = orc.attn_bwd_closed_form(*[x[b:b + 1].float().cpu() for x in (q, k, v, dout)])
+        _check((dq[b:b + 1], dk[b:b + 1], dv[b:b + 1]), refs)
+    dq2, dk2, dv2, _ = _cabi.bwd(dout, q, k, v, o, lse, min_workspace=True)
+    for a, c in ((dq, dq2), (dk, dk2), (dv, dv2)):
+        assert orc.rel_l2(a.float(), c.float()) < 6e-3
+    dq3, dk3, dv3, _ = _cabi.bwd(dout * 2, q, k, v, o, lse)
+    for a, c in ((dq, dq3), (dk, dk3), (dv, dv3)):
+        assert orc.rel_l2(c.float(), 2 * a.float()) < 1e-3
+    dq4, dk4, dv4, _ = _cabi.bwd(dout, q, k, v, o, lse)
+    assert torch.equal(dk, dk4) and torch.equal(dv, dv4)
+    assert orc.rel_l2(dq4.float(), dq.float()) < 1e-3
+
+
 @pytest.mark.parametrize("name", list(CASES))
 def test_backward_against_reference_golden_vectors(name):
     B, L, H, D, ts, qkn, seed = CASES[name]
