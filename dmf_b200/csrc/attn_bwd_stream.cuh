@@ -48,6 +48,10 @@ struct BwdStreamParams {
   float* dq_acc;        // workspace: per (b, h, query tile) 128 x head_dim floats as [column / 4][row][4]
   int32_t* status_word;
   int batch, heads, head_dim, seqlen_q, seqlen_kv;
+  // Heads whose rows start in the middle of a 32-byte sector (head_dim 72: rows of 144 bytes, every other head)
+  // are loaded 8 columns early, so that every 32-byte box is one sector instead of two halves: group 0 = q and k,
+  // group 1 = v and dout; (align0 + b * align_b + h * align_h) % 32 is the byte offset of the head's rows.
+  int align_enable[2], align0[2], align_b[2], align_h[2];
   int tiles_per_bh;     // key tiles per (b, h)
   int num_tiles;        // batch * heads * tiles_per_bh
   int steps;            // query tiles per (b, h)
@@ -143,11 +147,19 @@ __device__ __forceinline__ void issue_ds_blocks(bool leader, uint32_t d_tmem, ui
 
 // TMA load / store of a whole tile, block by block (columns beyond the head dim are filled with zeros on the way
 // in and clipped on the way out)
+// (shift = 8: the tile starts 8 columns before the head; those columns come back as zeros and head-dim column d
+// lies at tile column d + 8)
 template <typename TR>
 __device__ __forceinline__ void load_tile_blocks(uint32_t dst, const CUtensorMap* map, uint32_t bar, int row0, int h,
-                                                 int b) {
+                                                 int b, int shift) {
 #pragma unroll
-  for (int a = 0; a < TR::kAtoms; ++a) tma_load_4d(dst + a * TR::kAtomBytes, map, bar, 16 * a, row0, h, b);
+  for (int a = 0; a < TR::kAtoms; ++a) tma_load_4d(dst + a * TR::kAtomBytes, map, bar, 16 * a - shift, row0, h, b);
+}
+
+// 8 when the rows of head (b, h) of tensor group grp start in the middle of a 32-byte sector and may be shifted
+__device__ __forceinline__ int stream_shift(const BwdStreamParams& p, int grp, int b, int h) {
+  if (!p.align_enable[grp]) return 0;
+  return (((p.align0[grp] + b * p.align_b[grp] + h * p.align_h[grp]) & 31) == 16) ? 8 : 0;
 }
 template <typename TR>
 __device__ __forceinline__ void store_tile_blocks(const CUtensorMap* map, uint32_t src, int row0, int h, int b) {
@@ -330,6 +342,7 @@ attn_bwd_stream_kernel(const __grid_constant__ BwdStreamParams p) {
         const int k0 = (tile % p.tiles_per_bh) * 128;
         const int b = bh / p.heads, h = bh % p.heads;
         const int64_t row0 = (static_cast<int64_t>(b) * p.heads + h) * p.seqlen_q;
+        const int sqk = stream_shift(p, 0, b, h), svo = stream_shift(p, 1, b, h);
         for (int i = 0; ok && i < J; ++i, ++g) {
           const int q0 = i * 128;
           {  // Q_i with its two rows: the slot was freed by the last product of step g - 3
@@ -338,7 +351,7 @@ attn_bwd_stream_kernel(const __grid_constant__ BwdStreamParams p) {
             if (!ok) break;
             const uint32_t dst = s_q + sl * TR::kTileBytes, fb = bar(TR::kBarQFull + sl);
             mbar_arrive_expect_tx(fb, TR::kTileBytes + TR::kRowBytes);
-            load_tile_blocks<TR>(dst, &p.q, fb, q0, h, b);
+            load_tile_blocks<TR>(dst, &p.q, fb, q0, h, b, sqk);
             bulk_load_1d(s_rows + sl * TR::kRowBytes, p.nlse2 + row0 + q0, 512, fb);
             bulk_load_1d(s_rows + sl * TR::kRowBytes + 512, p.ndelta + row0 + q0, 512, fb);
             DMF_STRACE_EVENT(0, 1);
@@ -349,7 +362,7 @@ attn_bwd_stream_kernel(const __grid_constant__ BwdStreamParams p) {
             if (!ok) break;
             const uint32_t dst = s_do + sl * TR::kTileBytes, fb = bar(TR::kBarDoFull + sl);
             mbar_arrive_expect_tx(fb, TR::kTileBytes);
-            load_tile_blocks<TR>(dst, &p.dout, fb, q0, h, b);
+            load_tile_blocks<TR>(dst, &p.dout, fb, q0, h, b, svo);
             DMF_STRACE_EVENT(0, 2);
           }
           if (i == 0) {  // K_j, then V_j: free when every product of the previous key tile is complete (the first
@@ -358,9 +371,9 @@ attn_bwd_stream_kernel(const __grid_constant__ BwdStreamParams p) {
             if (!ok) break;
             const uint32_t fk = bar(TR::kBarKFull), fv = bar(TR::kBarVFull);
             mbar_arrive_expect_tx(fk, TR::kTileBytes);
-            load_tile_blocks<TR>(s_kv, &p.k, fk, k0, h, b);
+            load_tile_blocks<TR>(s_kv, &p.k, fk, k0, h, b, sqk);
             mbar_arrive_expect_tx(fv, TR::kTileBytes);
-            load_tile_blocks<TR>(s_kv + TR::kTileBytes, &p.v, fv, k0, h, b);
+            load_tile_blocks<TR>(s_kv + TR::kTileBytes, &p.v, fv, k0, h, b, svo);
             DMF_STRACE_EVENT(0, 3);
           }
         }
@@ -568,6 +581,10 @@ attn_bwd_stream_kernel(const __grid_constant__ BwdStreamParams p) {
       const int bh = tile / p.tiles_per_bh;
       const int k0 = (tile % p.tiles_per_bh) * 128;
       const int b = bh / p.heads, h = bh % p.heads;
+      // where the head's tiles were loaded 8 columns early, accumulator column c is head-dim column c - 8: the dQ
+      // partial and dK follow q and k, dV follows v and dout
+      const int sqk = stream_shift(p, 0, b, h), svo = stream_shift(p, 1, b, h);
+      const int gs = sqk >> 2;  // column groups of four to skip in the dQ partial
       for (int k = 0; k < J; ++k) {
         const uint32_t g = g0 + static_cast<uint32_t>(k);
         // the dQ partial -> registers, so that its columns can take the next dP at once
@@ -588,8 +605,8 @@ attn_bwd_stream_kernel(const __grid_constant__ BwdStreamParams p) {
         for (int c = 0; c < DPAD / 16; ++c) {
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4)
-            if (c * 4 + q4 < groups && !(kStreamDiag & 2))
-              red_add_v4(acc + (c * 4 + q4) * 512, a[c][4 * q4], a[c][4 * q4 + 1], a[c][4 * q4 + 2], a[c][4 * q4 + 3]);
+            if (c * 4 + q4 >= gs && c * 4 + q4 - gs < groups && !(kStreamDiag & 2))
+              red_add_v4(acc + (c * 4 + q4 - gs) * 512, a[c][4 * q4], a[c][4 * q4 + 1], a[c][4 * q4 + 2], a[c][4 * q4 + 3]);
         }
         if (warp == 10) DMF_STRACE_EVENT(3, 51);
       }
@@ -615,10 +632,12 @@ attn_bwd_stream_kernel(const __grid_constant__ BwdStreamParams p) {
           p1[i] = Pack2<T>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
         }
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const uint32_t off = chunk_off(c * 16 + hh * 8);
-          *reinterpret_cast<uint4*>(dk_stage + off) = make_uint4(p0[4 * hh], p0[4 * hh + 1], p0[4 * hh + 2], p0[4 * hh + 3]);
-          *reinterpret_cast<uint4*>(dv_stage + off) = make_uint4(p1[4 * hh], p1[4 * hh + 1], p1[4 * hh + 2], p1[4 * hh + 3]);
+        for (int hh = 0; hh < 2; ++hh) {  // the staged tiles are NOT shifted (a store must not start left of column 0)
+          const int ck = c * 16 + hh * 8 - sqk, cv = c * 16 + hh * 8 - svo;
+          if (ck >= 0)
+            *reinterpret_cast<uint4*>(dk_stage + chunk_off(ck)) = make_uint4(p0[4 * hh], p0[4 * hh + 1], p0[4 * hh + 2], p0[4 * hh + 3]);
+          if (cv >= 0)
+            *reinterpret_cast<uint4*>(dv_stage + chunk_off(cv)) = make_uint4(p1[4 * hh], p1[4 * hh + 1], p1[4 * hh + 2], p1[4 * hh + 3]);
         }
       }
       tc_fence_before_sync();

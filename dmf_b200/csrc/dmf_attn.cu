@@ -590,6 +590,25 @@ int run_bwd_stream(const dmf_attn_bwd_args* a, int tail, int sm_count) {
   p.steps = Lq / 128;
   p.scale = a->softmax_scale;
   p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
+  if (D == 72) {
+    // head rows of 144 bytes straddle 32-byte sectors on every other head: let the kernel start its boxes 8 columns
+    // early there (the tile has 80 columns).  Both tensors of a group must agree on the alignment pattern.
+    auto pattern = [](const dmf_attn_tensor& t, int* out) -> bool {
+      if ((t.stride_l * 2) % 32 != 0) return false;  // alignment must not change along the sequence
+      out[0] = static_cast<int>(reinterpret_cast<uintptr_t>(t.ptr) & 31);
+      out[1] = static_cast<int>((t.stride_b * 2) & 31);
+      out[2] = static_cast<int>((t.stride_h * 2) & 31);
+      return true;
+    };
+    const dmf_attn_tensor* pairs[2][2] = {{&a->q, &a->k}, {&a->v, &a->dout}};
+    for (int g = 0; g < 2; ++g) {
+      int ref[3] = {0, 0, 0}, cur[3] = {0, 0, 0};
+      const bool same = pattern(*pairs[g][0], ref) && pattern(*pairs[g][1], cur) && cur[0] == ref[0] &&
+                        cur[1] == ref[1] && cur[2] == ref[2];
+      p.align_enable[g] = same ? 1 : 0;
+      p.align0[g] = ref[0]; p.align_b[g] = ref[1]; p.align_h[g] = ref[2];
+    }
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   if (cudaMemsetAsync(p.dq_acc, 0, sizeof(float) * static_cast<size_t>(B) * H * Lq * D, stream) != cudaSuccess) {
     (void)cudaGetLastError();

@@ -111,6 +111,16 @@ def test_long_sequence_one_pass_backward_ragged_lengths_fp16(shape):
     _check((dq, dk, dv), orc.attn_bwd_closed_form(q.float(), k.float(), v.float(), dout.float()), tol=1e-3)
 
 
+@pytest.mark.parametrize("H", [3, 4])
+def test_long_sequence_backward_packed_layout(H):
+    """q, k, v as strided views of one packed (B, L, 3, H, 72) projection: with head_dim 72 every other head starts
+    in the middle of a 32-byte sector and its tiles are loaded 8 columns early; with an odd number of heads the
+    pattern of q / k differs from that of v, and from dout's (contiguous)."""
+    q, k, v, _, _, _, dout = (x.bfloat16() for x in orc.make_inputs(2, 384, H, 72, seed=40 + H, n_extra=1))
+    _, _, dq, dk, dv = _fwd_bwd((q, k, v), dout, layout="packed")
+    _check((dq, dk, dv), orc.attn_bwd_closed_form(q.float(), k.float(), v.float(), dout.float()))
+
+
 @pytest.mark.parametrize("cfg", ["C2", "C3"])
 def test_backward_full_size_properties(cfg):
     """At the full benchmark sizes: batch slices against the oracle, the one-pass kernel of the shape against the
