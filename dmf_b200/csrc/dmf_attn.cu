@@ -451,7 +451,8 @@ int launch_bwd_tail(const BwdParams& p, int tail, int grid, cudaStream_t stream)
 
 // ---- backward in one pass (two-tile sequences, head_dim <= 80) ----
 
-// DMF_ATTN_BWD_FUSED=0 in the environment keeps the two-launch backward (for comparisons).
+// DMF_ATTN_BWD_FUSED=0 in the environment takes this kernel out (for comparisons): two-tile sequences then go the
+// way of longer ones.
 bool bwd_fused_enabled() {
   static const bool enabled = [] {
     const char* e = std::getenv("DMF_ATTN_BWD_FUSED");
