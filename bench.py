@@ -125,7 +125,7 @@ def _pin_to_gpu_numa_node(dev_index):
 class ClockSampler(threading.Thread):
     """Reads (never sets) SM clock and throttle reasons through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.002):
+    def __init__(self, index: int, period_s: float = 0.001):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz, self.uuid = [], set(), None, None
@@ -154,13 +154,24 @@ class ClockSampler(threading.Thread):
                 "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
                 "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
             }
+            def read_reasons():
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+
+            n, was_active = 0, False
             while not self._stop_evt.is_set():
                 if self.active.is_set():
+                    # the clock every time round (one NVML call: a short timed region still gets several samples),
+                    # the throttle reasons every fourth time and once more when the window closes
                     self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                    for k, bit in names.items():
-                        if mask & bit:
-                            self.reasons.add(k)
+                    if n % 4 == 0:
+                        read_reasons()
+                    n, was_active = n + 1, True
+                elif was_active:
+                    read_reasons()
+                    n, was_active = 0, False
                 time.sleep(self.period)
         except Exception as e:  # NVML missing: report, do not fail the bench
             self.error = repr(e)
